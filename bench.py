@@ -9,26 +9,45 @@ BASELINE configurations (seeded synthetic inputs of their shapes):
 
   c4 (default)  prefix-prefill, 8B geometry, bf16, 8 requests x 65536 cached
                 tokens (128 documents x 512 at random slots) + 512 new tokens;
-                N > 1 shards by KV-head group and all-gathers the outputs.
+                N > 1 shards by KV-head group and gathers the outputs.
   c5            decode, 8B geometry, 256 sequences x 4k..16k cached tokens,
                 e4m3 KV, bf16 query; N > 1 shards by request.
   c3, c2        the smaller prefill configurations (1 GPU).
 
-One JSON line is printed by rank 0.  ``value`` is query tokens per second with
-all inputs resident in HBM (the call's launches replayed from a CUDA graph
-unless ``--cuda-graph off``); ``e2e`` is the same call through the public API
-with the step's activations and metadata copied from pinned host memory and
-the output copied back, every step - measured in sequence on one stream and as
-a three-stream pipeline over two buffer sets, the better of the two reported.
-Timing is CUDA events on the launching stream, max over ranks.  ``--impl reference`` times the CPU oracle (a float32
-torch restatement of the reference kernels) on a bounded sample with all host
-threads.
+One JSON line is printed by rank 0: the headline workload (c4 unless
+``--workload`` says otherwise) with, under ``also``, the decode workload c5 at
+the same N (sharded by request) and, at N = 1, the ragged prefill workload c3,
+each with its own value, roofline and end-to-end figure.  At N = 1 the line
+also carries ``triton_baseline``: the reference's own Triton kernels compiled
+for this GPU and timed on the same inputs (outside every timed region of this
+library).  At N > 1 one step of the output gather fused into the kernels is
+compared bit for bit with the same kernels followed by an NCCL all-gather
+before anything is timed (``gather_check``; a mismatch ends the run non-zero).
+
+``value`` is query tokens per second of the whole job with all inputs resident
+in HBM (the call's launches replayed from a CUDA graph unless ``--cuda-graph
+off``; the eager cost of the same call through the Python wrapper is reported
+beside it as ``execution.eager_ms_per_step``).  A call sharded by KV-head group
+processes every token on every rank, so its tokens are counted once, not once
+per rank.  ``e2e`` is the same call through the public API with the step's
+activations and metadata copied from pinned host memory and the result copied
+back, every step - measured in sequence on one stream and as a three-stream
+pipeline over two buffer sets, the better of the two reported; at N > 1 every
+rank uploads its own shard and reads back its 1/N slice of the gathered rows,
+so the job reads the result back once.  Timing is CUDA events on the launching
+stream, max over ranks.
+
+``--impl reference`` times the CPU oracle (a float32 torch restatement of the
+reference kernels) with all host threads; each step is one call over a bounded
+sample of the workload made of whole requests / sequences with their full
+context, so its tokens per second need no extrapolation.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -39,6 +58,8 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 import torch  # noqa: E402
+
+METRIC = "deferred-RoPE attention throughput (query tokens/s per attention-layer call)"
 
 
 def parse_args():
@@ -57,6 +78,8 @@ def parse_args():
                     help="shrink the workload (profiling captures only; not a bench value)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-also", action="store_true", help="only the headline workload")
+    ap.add_argument("--no-triton", action="store_true", help="skip the Triton reference leg")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: 'fused' = the kernels store their result rows into every rank's output "
                          "buffer (peer-mapped memory) and the step ends with a barrier; 'nccl' = all-gather")
@@ -76,6 +99,17 @@ def peaks():
         return dict(hbm=float(d["hbm_gbs"]), tf_burst=float(d["bf16_tflops"]),
                     tf_sust=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), src="measured")
     return dict(hbm=6650.0, tf_burst=1590.0, tf_sust=1400.0, src="fallback")
+
+
+def recorded_traffic(name):
+    """DRAM bytes per launch of the workload's dominant kernel as recorded in the ncu summary
+    under profiles/ (a line ``dram_traffic_bytes_per_launch[<workload>]: <number>``), or None."""
+    pat = re.compile(r"dram_traffic_bytes_per_launch\[" + re.escape(name) + r"\]\s*:\s*([0-9.eE+]+)")
+    for f in sorted((ROOT / "profiles").glob("*.md")):
+        m = pat.search(f.read_text())
+        if m:
+            return float(m.group(1))
+    return None
 
 
 L2_LARGE = "inputs larger than L2 (no flush)"
@@ -107,10 +141,18 @@ def workload_info(name, world=1, scale=1.0, kv_dtype="auto"):
     raise KeyError(name)
 
 
+def c5_documents(nseq):
+    """Document lists and cache scales of the decode workload (seeded)."""
+    import numpy as np
+    rng = np.random.default_rng(0)
+    docs = [[512] * int(rng.integers(8, 33)) for _ in range(nseq)]
+    ks, vs = float(rng.uniform(0.05, 0.2)), float(rng.uniform(0.05, 0.2))
+    return docs, ks, vs
+
+
 def build_workload(name, device, variant, rank=0, world=1, scale=1.0, kv_dtype="auto"):
     """Returns (case, info).  For world > 1 the returned case is this rank's shard."""
     from lazy_attention_b200 import synth
-    import numpy as np
     if name == "c4":
         batch = 8
         ndocs = max(1, int(round(128 * scale)))
@@ -126,9 +168,7 @@ def build_workload(name, device, variant, rank=0, world=1, scale=1.0, kv_dtype="
         case = synth.config_c2(device=device, variant=variant)
     elif name == "c5":
         nseq = max(world, int(round(256 * scale)))
-        rng = np.random.default_rng(0)
-        docs = [[512] * int(rng.integers(8, 33)) for _ in range(nseq)]
-        ks, vs = float(rng.uniform(0.05, 0.2)), float(rng.uniform(0.05, 0.2))
+        docs, ks, vs = c5_documents(nseq)
         mine = list(range(nseq))
         if world > 1:
             from lazy_attention_b200.sharding import lpt_assign
@@ -144,7 +184,7 @@ def build_workload(name, device, variant, rank=0, world=1, scale=1.0, kv_dtype="
 
 
 def algorithmic_work(case, info):
-    """FLOPs and bytes one call must do/move (this rank's shard)."""
+    """FLOPs and bytes one call must do/move, and the query tokens it serves (this rank's shard)."""
     g = case["geom"]
     Hq, Hkv, D, BS = g.num_q_heads, g.num_kv_heads, g.head_dim, g.block_size
     e_q = case["q"].element_size()
@@ -210,14 +250,15 @@ def make_step(case, info, kernel):
                                                       value_cache=case["v_cache"], block_table=t["block_table"],
                                                       query_start_loc=t["query_start_loc"],
                                                       seq_lens=t["seq_lens"], max_query_len=1,
-                                                      q_offset=t["q_offset"], q_mask=t["q_mask"], peer_out=peer_out, **common)
+                                                      q_offset=t["q_offset"], q_mask=t["q_mask"],
+                                                      peer_out=peer_out, **common)
         return o
 
     return step, out
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle sampling during the timed region."""
+    """nvidia-smi clock / throttle sampling during the timed region (queries only)."""
 
     def __init__(self, index):
         self.index, self.rows, self.proc = index, [], None
@@ -310,128 +351,167 @@ def time_steps(fn, steps, warmup, device, world, flush=False):
 # --------------------------------------------------------------------------------------
 # CPU baseline (oracle port of the reference kernels)
 # --------------------------------------------------------------------------------------
-def cpu_baseline(name, variant, budget_s=12.0):
-    """Times the float32 torch oracle on a bounded sample of the workload with all
-    host threads; returns tokens/s scaled by the sample's share of the work."""
-    sys.path.insert(0, str(ROOT / "tests"))
-    import util
+def cpu_sample(name, variant):
+    """A bounded sample of the workload for the CPU oracle: whole requests / sequences with
+    their full context and all heads, so that tokens per second of the sample is the rate of
+    the workload.  Returns (run, tokens, description)."""
+    from oracle import runner
     from lazy_attention_b200 import synth
-    import numpy as np
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
     if name == "c4":
-        case = synth.config_c4(device="cpu", variant=variant, batch=1, num_docs=32)
-        sample = "1 of 8 requests, all heads, 32 of 128 documents (16384 cached tokens), 512 new tokens"
+        case = synth.config_c4(device="cpu", variant=variant, batch=1, qlen=128)
+        sample = ("1 of the 8 requests with its full context (128 x 512 cached tokens, all 32 heads) and 128 of "
+                  "its 512 new tokens, one KV head after the other")
         op = "lazy_prefill" if variant == "lazy" else "mepic_prefill"
+        run = lambda: runner.run_oracle_by_kv_head(case, op)  # noqa: E731
+        tokens = 128
     elif name == "c3":
-        case = synth.config_c3(device="cpu", variant=variant, batch=1)
-        sample = "1 of 32 requests, all heads"
+        case = synth.config_c3(device="cpu", variant=variant, batch=2)
+        sample = "2 requests drawn as the workload's 32 are (20 documents each, all heads)"
         op = "lazy_prefill" if variant == "lazy" else "mepic_prefill"
+        run = lambda: runner.run_oracle_by_kv_head(case, op)  # noqa: E731
+        tokens = sum(case["q_lens"])
     elif name == "c2":
         case = synth.config_c2(device="cpu", variant=variant)
         sample = "the whole call"
         op = "lazy_prefill" if variant == "lazy" else "mepic_prefill"
+        run = lambda: runner.run_oracle(case, op)  # noqa: E731
+        tokens = 128
     else:
-        rng = np.random.default_rng(0)
-        docs = [[512] * int(rng.integers(8, 33)) for _ in range(4)]
-        case = synth.build_decode(synth.GEOM_8B, torch.bfloat16, docs, seed=0, device="cpu",
-                                  kv_dtype="fp8_e4m3", variant=variant, k_scale=0.1, v_scale=0.1)
-        sample = "4 of 256 sequences, all heads"
+        docs, ks, vs = c5_documents(256)
+        case = synth.build_decode(synth.GEOM_8B, torch.bfloat16, docs[:8], seed=0, device="cpu",
+                                  kv_dtype="fp8_e4m3", variant=variant, k_scale=ks, v_scale=vs)
+        sample = "the first 8 of the 256 sequences (all heads, full context)"
         op = "lazy_op" if variant == "lazy" else "mepic_op"
-    case["packed_block_table"] = util.pack_host(case)
-    info = dict(kind="decode" if name == "c5" else "prefill")
-    flops, _, units = algorithmic_work(case, info)
-    util.run_oracle(case, op)  # warm-up
+        run = lambda: runner.run_oracle(case, op)  # noqa: E731
+        tokens = 8
+    case["packed_block_table"] = runner.pack_host(case)
+    return run, tokens, sample
+
+
+def cpu_baseline(name, variant, budget_s=12.0):
+    """Times the float32 torch oracle on the bounded sample with all host threads."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    run, tokens, sample = cpu_sample(name, variant)
+    run()  # warm-up
     t0 = time.perf_counter()
     n = 0
     while True:
-        util.run_oracle(case, op)
+        run()
         n += 1
         if time.perf_counter() - t0 > budget_s or n >= 50:
             break
     dt = (time.perf_counter() - t0) / n
-    return dict(seconds_per_call=dt, flops=flops, units=units, cores=cores, sample=sample)
+    return dict(value=tokens / dt, unit="tokens/s", cores=cores, kind="port",
+                sample=f"{sample}; {n} calls of {dt:.2f} s")
 
 
 def reference_arm(args):
+    """K timed steps (after warm-up) of the CPU oracle, each step one call over the bounded
+    sample; rank 0 only."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    case_flops = cpu_baseline(args.workload, args.variant)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    run, tokens, sample = cpu_sample(args.workload, args.variant)
+    for _ in range(max(1, min(args.warmup, 3))):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        run()
+    dt = (time.perf_counter() - t0) / args.steps
     winfo = workload_info(args.workload, int(os.environ.get("WORLD_SIZE", "1")), args.scale, args.kv_dtype)
-    # Scale the sample's rate to whole-workload tokens/s through its FLOP share.
-    full_flops, full_units = full_workload_flops(args.workload)
-    tok_s = full_units / (case_flops["seconds_per_call"] * full_flops / case_flops["flops"])
-    line = dict(metric="deferred-RoPE attention throughput (query tokens/s per attention-layer call)",
-                impl="reference", value=tok_s, unit="tokens/s", n_gpus=args.gpus, steps=args.steps,
-                warmup=args.warmup, ms_per_step=1e3 * full_units / tok_s, higher_is_better=True,
+    tok_s = tokens / dt
+    line = dict(metric=METRIC, impl="reference", value=tok_s, unit="tokens/s", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=1e3 * dt, tokens_per_step=tokens, higher_is_better=True,
                 scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
                 config=dict(workload=winfo["workload"], variant=args.variant, kernel=args.kernel,
                             partition=winfo["partition"], l2=winfo["l2"]),
-                cpu_baseline=dict(value=tok_s, unit="tokens/s", cores=case_flops["cores"], kind="port",
-                                  sample=case_flops["sample"] + "; rate scaled to the full call by FLOPs"),
+                cpu_baseline=dict(value=tok_s, unit="tokens/s", cores=cores, kind="port",
+                                  sample=sample + "; each step is one call over this sample"),
                 e2e=dict(value=tok_s, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line))
 
 
-def full_workload_flops(name):
-    """Algorithmic FLOPs and token count of the full-size call (no tensors built)."""
-    import numpy as np
-    Hq, D = 32, 128
-    if name == "c4":
-        return 8 * 4.0 * Hq * D * (512 * 65536 + 512 * 513 / 2), 8 * 512
-    if name == "c2":
-        return 4.0 * 32 * 64 * (128 * 5120 + 128 * 129 / 2), 128
-    if name == "c5":
-        rng = np.random.default_rng(0)
-        L = [512 * int(rng.integers(8, 33)) + 1 for _ in range(256)]
-        return sum(4.0 * Hq * D * l for l in L), 256
-    from lazy_attention_b200 import synth
-    rng = np.random.default_rng(0)
-    pool = [int(n) for n in rng.integers(256, 1025, size=200)]
-    draws = synth.zipf_requests(32, 200, 20, 1.1, rng)
-    fl, tok = 0.0, 0
-    for d in draws:
-        q = int(rng.integers(64, 257))
-        fl += 4.0 * Hq * D * (q * sum(pool[i] for i in d) + q * (q + 1) / 2)
-        tok += q
-    return fl, tok
+# --------------------------------------------------------------------------------------
+# the reference's Triton kernels on this GPU (a baseline beside the timed regions, N = 1)
+# --------------------------------------------------------------------------------------
+def triton_baseline(case, info, ours_out, steps=3):
+    sys.path.insert(0, str(ROOT / "baseline"))
+    try:
+        import triton_ref
+        why = triton_ref.available()
+        if why:
+            return dict(unavailable=why)
+        lazy = case["variant"] == "lazy"
+        if info["kind"] == "prefill":
+            op = "lazy_prefill" if lazy else "mepic_prefill"
+        else:
+            op = "lazy_op" if lazy else "mepic_op"
+        out = torch.zeros_like(ours_out)
+        t0 = time.perf_counter()
+        triton_ref.run(case, op, out=out)          # compiles on first use
+        torch.cuda.synchronize()
+        first_s = time.perf_counter() - t0
+        triton_ref.run(case, op, out=out)
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        ev[0].record()
+        for i in range(steps):
+            triton_ref.run(case, op, out=out)
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        ms = ev[0].elapsed_time(ev[-1]) / steps
+        diff = float((out.float() - ours_out.float()).abs().max().item())
+        import triton
+        return dict(ms_per_step=ms, steps=steps, first_call_s=first_s, max_abs_diff_vs_this_library=diff,
+                    what="the reference's Triton operator with its own launch parameters, compiled by Triton "
+                         f"{triton.__version__} for this GPU, same inputs, eager calls")
+    except Exception as e:  # the baseline is optional: report why it is missing
+        torch.cuda.synchronize()
+        return dict(unavailable=f"{type(e).__name__}: {str(e)[:300]}")
 
 
 # --------------------------------------------------------------------------------------
-def main():
-    args = parse_args()
-    if args.impl == "reference":
-        reference_arm(args)
-        return
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (the library has no CPU path)")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
+def run_workload(name, args, world, rank, local_rank, device):
+    """Builds one workload on this rank, checks the gather (N > 1), times it device-resident
+    and end to end, and returns the result fields (meaningful on rank 0)."""
     import torch.distributed as dist
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
     import lazy_attention_b200 as la
     from lazy_attention_b200 import sharding
 
-    case, info = build_workload(args.workload, device, args.variant, rank, world, args.scale, args.kv_dtype)
+    case, info = build_workload(name, device, args.variant, rank, world, args.scale, args.kv_dtype)
     flops, byts, units = algorithmic_work(case, info)
     step, out = make_step(case, info, args.kernel)
     g = case["geom"]
+    steps, warmup = args.steps, args.warmup
 
-    # N > 1: how the ranks' results come together
-    gather_mode, peers = "none", None
+    # ---- the job's totals.  A call sharded by KV-head group serves every token on every rank:
+    # its tokens are counted once; FLOPs and bytes are partitioned and add up.
+    tokens_all = units
+    if world > 1 and info["partition"] == "request":
+        t = torch.tensor([units], dtype=torch.float64, device=device)
+        dist.all_reduce(t)
+        tokens_all = int(t[0].item())
+
+    def nccl_gather(o):
+        if info["kind"] == "prefill":
+            return sharding.gather_head_outputs(o, world)
+        docs, _, _ = c5_documents(info["total_seqs"])
+        rows = sharding.lpt_assign([sum(d) + 1 for d in docs], world)
+        return sharding.gather_request_outputs(o, rows, info["total_seqs"])
+
+    # ---- N > 1: how the ranks' results come together
+    gather_mode, peers, gather_check = "none", None, None
     if world > 1 and args.gather == "fused":
         try:
             if info["kind"] == "prefill":
-                mk = lambda: sharding.PeerOutput(case["num_tokens"], info["full_heads"][0], g.head_dim, out.dtype,
-                                                 device, head_offset=rank * g.num_q_heads)
+                mk = lambda: sharding.PeerOutput(case["num_tokens"], info["full_heads"][0], g.head_dim,  # noqa: E731
+                                                 out.dtype, device, head_offset=rank * g.num_q_heads)
             else:
-                mk = lambda: sharding.PeerOutput(info["total_seqs"], g.num_q_heads, g.head_dim, out.dtype, device,
-                                                 row_map=case["global_rows"])
+                mk = lambda: sharding.PeerOutput(info["total_seqs"], g.num_q_heads, g.head_dim, out.dtype,  # noqa: E731
+                                                 device, row_map=case["global_rows"])
             peers = [mk(), mk()]  # two sets: a step's result is read while the next step is written
             gather_mode = "fused into the kernels (peer stores over NVLink) + barrier"
         except Exception as e:
@@ -439,26 +519,47 @@ def main():
             gather_mode = f"nccl all-gather (peer buffers unavailable: {type(e).__name__})"
     elif world > 1:
         gather_mode = "nccl all-gather"
+    if peers is not None:
+        # correctness gate: the rows the peers stored must equal, bit for bit, what the same
+        # kernels write locally followed by an all-gather
+        want = nccl_gather(step(peer_out=None).clone())
+        ok = 1
+        for pset in peers:
+            pset.local.zero_()
+            torch.cuda.synchronize(device)
+            dist.barrier()
+            step(peer_out=pset)
+            pset.barrier()
+            torch.cuda.synchronize(device)
+            ok &= int(torch.equal(pset.local, want))
+        flag = torch.tensor([ok], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        gather_check = "bit-exact" if int(flag.item()) == 1 else "MISMATCH"
+        if gather_check != "bit-exact":
+            if rank == 0:
+                print(json.dumps(dict(error=f"{name}: fused output gather differs from the all-gather")))
+            raise SystemExit(3)
 
-    # One call's launches (attention kernel + split merge) captured once and replayed: the
-    # Python wrapper's argument marshalling then costs nothing per step, which matters for the
-    # sub-millisecond calls (decode, c2, 8-GPU shards).  Collectives stay outside the graph.
+    # ---- one call's launches (attention kernel + split merge) captured once and replayed: the
+    # Python wrapper's argument marshalling then costs nothing per step.  Collectives stay outside.
     launch_mode, launches_per_step = "eager", None
-    def fast_step():
+
+    def eager_step():
         return step(peer_out=peers[0] if peers else None)
+    fast_step = eager_step
     if args.cuda_graph == "on":
         try:
             side = torch.cuda.Stream(device)
             side.wait_stream(torch.cuda.current_stream(device))
             with torch.cuda.stream(side):
                 for _ in range(2):
-                    step(peer_out=peers[0] if peers else None)
+                    eager_step()
             torch.cuda.current_stream(device).wait_stream(side)
             torch.cuda.synchronize(device)
             graph = torch.cuda.CUDAGraph()
             n0 = la.launch_count()
             with torch.cuda.graph(graph):
-                step(peer_out=peers[0] if peers else None)
+                eager_step()
             launches_per_step = la.launch_count() - n0
 
             def fast_step():
@@ -473,21 +574,9 @@ def main():
         def post(o, slot=0):
             peers[slot].barrier()
             return peers[slot].local
-    elif world > 1 and info["kind"] == "prefill":
-        def post(o, slot=0):
-            return sharding.gather_head_outputs(o, world)
     elif world > 1:
-        counts = torch.tensor([units], device=device)
-        allc = [torch.zeros_like(counts) for _ in range(world)]
-        dist.all_gather(allc, counts)
-        cap = max(int(c.item()) for c in allc)
-        buf = torch.zeros((cap, g.num_q_heads, g.head_dim), dtype=out.dtype, device=device)
-        gathered = torch.empty((world * cap, g.num_q_heads, g.head_dim), dtype=out.dtype, device=device)
-
         def post(o, slot=0):
-            buf[:o.shape[0]] = o
-            dist.all_gather_into_tensor(gathered, buf)
-            return gathered
+            return nccl_gather(o)
     else:
         def post(o, slot=0):
             return o
@@ -501,45 +590,39 @@ def main():
     flush = byts < 200e6
     launches0 = la.launch_count()
     with ClockSampler(local_rank) as clk:
-        total_ms, per = time_steps(full_step, args.steps, args.warmup, device, world, flush)
-    launches = la.launch_count() - launches0 - 0
-    launches_timed = int(round(launches * args.steps / (args.steps + args.warmup)))
+        total_ms, per = time_steps(full_step, steps, warmup, device, world, flush)
+    launches = la.launch_count() - launches0
+    launches_timed = int(round(launches * steps / (steps + warmup)))
     if launches_per_step is not None:
-        launches_timed = launches_per_step * args.steps
-    units_all = units
-    flops_all, byts_all = flops, byts
-    if world > 1:
-        t = torch.tensor([units, flops, byts], dtype=torch.float64, device=device)
-        dist.all_reduce(t)
-        units_all, flops_all, byts_all = int(t[0].item()), float(t[1].item()), float(t[2].item())
-    ms_per_step = total_ms / args.steps
-    value = units_all / (ms_per_step * 1e-3)
+        launches_timed = launches_per_step * steps
+    ms_per_step = total_ms / steps
+    value = tokens_all / (ms_per_step * 1e-3)
+    assert abs(value * ms_per_step * 1e-3 - tokens_all) < 1.0
 
-    # ---- kernel-only time of this rank's attention call (roofline) ------------------------
-    _, kper = time_steps(fast_step, args.steps, 1, device, 1, flush)
+    # ---- kernel-only time of this rank's attention call (roofline), replayed and eager ---------
+    _, kper = time_steps(fast_step, steps, 1, device, 1, flush)
     kern_ms = sum(kper) / len(kper)
+    _, eper = time_steps(eager_step, steps, 2, device, 1, flush)
+    eager_ms = sum(eper) / len(eper)
     pk = peaks()
-    # DRAM bytes per launch of the dominant kernel from an ncu capture (dram__bytes_read.sum +
-    # dram__bytes_write.sum) of a 1/8-size case, scaled to the full launch by the cached bytes;
-    # the captures are summarised under profiles/.  Only quoted for the exact configuration captured.
     traffic = None
     if (world == 1 and args.scale == 1.0 and args.variant == "lazy" and args.kernel == "auto"
             and args.kv_dtype == "auto"):
-        traffic = {"c4": 2.31e9, "c5": 5.57e9}.get(args.workload)
+        traffic = recorded_traffic(name)
     if info["kind"] == "prefill":
         achieved = flops / (kern_ms * 1e-3) / 1e12
         peak = pk["tf_burst"]
         roof = dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak,
                     traffic=traffic, peak_kind="burst bf16 (cuBLAS), " + pk["src"],
                     frac_of_sustained_peak=achieved / pk["tf_sust"], frac_of_nominal_2250=achieved / 2250.0,
-                    kernel_ms=kern_ms,
-                    algorithmic_flops=flops, algorithmic_bytes=byts)
+                    kernel_ms=kern_ms, algorithmic_flops=flops, algorithmic_bytes=byts)
     else:
         achieved = byts / (kern_ms * 1e-3) / 1e9
         roof = dict(bound="hbm", achieved=achieved, peak=pk["hbm"], unit="GB/s", frac=achieved / pk["hbm"],
                     traffic=traffic, peak_kind="copy bandwidth, " + pk["src"], frac_of_nominal_8000=achieved / 8000.0,
-                    kernel_ms=kern_ms,
-                    algorithmic_flops=flops, algorithmic_bytes=byts)
+                    kernel_ms=kern_ms, algorithmic_flops=flops, algorithmic_bytes=byts)
+    if world > 1:
+        roof["scope"] = "rank 0's shard: its kernel time against its share of the work"
 
     # ---- end to end through the public API with host buffers ----------------------------
     e2e = None
@@ -553,10 +636,16 @@ def main():
         dtab = {n: torch.empty_like(case[n]) for n in tkeys}
         res = full_step()
         torch.cuda.synchronize(device)
-        hout = torch.empty(res.shape, dtype=res.dtype).pin_memory()
+        # the job reads the gathered result back once: rank r takes rows [r0, r1)
+        r0, r1 = res.shape[0] * rank // world, res.shape[0] * (rank + 1) // world
+        hout = torch.empty((r1 - r0,) + tuple(res.shape[1:]), dtype=res.dtype).pin_memory()
         h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv)) + \
             sum(t.numel() * t.element_size() for t in htab.values())
         d2h = hout.numel() * hout.element_size()
+        if world > 1:
+            t = torch.tensor([h2d, d2h], dtype=torch.float64, device=device)
+            dist.all_reduce(t)
+            h2d, d2h = int(t[0].item()), int(t[1].item())
 
         def e2e_step():
             dq.copy_(hq, non_blocking=True)
@@ -564,10 +653,10 @@ def main():
             dv.copy_(hv, non_blocking=True)
             for n in tkeys:
                 dtab[n].copy_(htab[n], non_blocking=True)
-            hout.copy_(full_step(dq, dk, dv, dtab), non_blocking=True)
+            hout.copy_(full_step(dq, dk, dv, dtab)[r0:r1], non_blocking=True)
 
-        e_total, _ = time_steps(e2e_step, args.steps, args.warmup, device, world, flush)
-        serial_ms = e_total / args.steps
+        e_total, _ = time_steps(e2e_step, steps, warmup, device, world, flush)
+        serial_ms = e_total / steps
 
         # The same steps as a pipeline: two sets of device buffers, uploads on one stream, the
         # call on the current stream, the read-back on a third, so that a step's copies run
@@ -580,7 +669,7 @@ def main():
         for _ in range(2):
             sets.append(dict(q=torch.empty_like(case["q"]), k=torch.empty_like(case["k"]),
                              v=torch.empty_like(case["v"]), tab={n: torch.empty_like(case[n]) for n in tkeys},
-                             out=torch.empty_like(out), host=torch.empty(res.shape, dtype=res.dtype).pin_memory(),
+                             out=torch.empty_like(out), host=torch.empty_like(hout).pin_memory(),
                              up=torch.cuda.Event(), done=torch.cuda.Event(), down=torch.cuda.Event()))
 
         def pipelined(n_steps):
@@ -596,19 +685,17 @@ def main():
                     b["up"].record(s_up)
                 cur.wait_event(b["up"])
                 cur.wait_event(b["down"])            # the previous result in this buffer has been read back
-                if world > 1:                        # the gathered result lives in one shared buffer
-                    cur.wait_event(sets[(i + 1) % 2]["down"])
                 r = full_step(b["q"], b["k"], b["v"], b["tab"], out_=b["out"], slot=i % 2)
                 b["done"].record(cur)
                 with torch.cuda.stream(s_down):
                     s_down.wait_event(b["done"])
-                    b["host"].copy_(r, non_blocking=True)
+                    b["host"].copy_(r[r0:r1], non_blocking=True)
                     r.record_stream(s_down)
                     b["down"].record(s_down)
             for b in sets:
                 cur.wait_event(b["down"])
 
-        pipelined(args.warmup)
+        pipelined(warmup)
         torch.cuda.synchronize(device)
         if world > 1:
             dist.barrier()
@@ -616,7 +703,7 @@ def main():
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record(cur)
         s_up.wait_event(ev0)
-        pipelined(args.steps)
+        pipelined(steps)
         ev1.record(cur)
         torch.cuda.synchronize(device)
         p_total = ev0.elapsed_time(ev1)
@@ -625,31 +712,77 @@ def main():
             tt = torch.tensor([p_total], dtype=torch.float64, device=device)
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             p_total = float(tt.item())
-        piped_ms = p_total / args.steps
+        piped_ms = p_total / steps
         best_ms = min(piped_ms, serial_ms)
-        e2e = dict(value=units_all / (best_ms * 1e-3), unit="tokens/s",
+        e2e = dict(value=tokens_all / (best_ms * 1e-3), unit="tokens/s",
                    h2d_bytes_per_step=int(h2d), d2h_bytes_per_step=int(d2h), ms_per_step=best_ms,
                    serial_ms_per_step=serial_ms, pipelined_ms_per_step=piped_ms,
                    mode="uploads and read-backs pipelined under the neighbouring steps' calls"
                    if piped_ms <= serial_ms else "upload, call and read-back in sequence on one stream")
 
+    res = dict(value=value, unit="tokens/s", ms_per_step=ms_per_step, tokens_per_step=tokens_all,
+               scaling=info["scaling"],
+               dtype="bf16" if info["kind"] == "prefill" and "fp8" not in args.kv_dtype else
+               f"bf16 query, {case['kv_cache_dtype'].replace('auto', 'bf16').replace('fp8_', '')} KV, f32 accumulate",
+               config=dict(workload=info["workload"], variant=args.variant, kernel=args.kernel,
+                           partition=info["partition"], l2=info["l2"]),
+               execution=dict(launch=launch_mode, gather=gather_mode, eager_ms_per_step=eager_ms,
+                              replay_ms_per_step=kern_ms),
+               roofline=roof, e2e=e2e, gpu_launches=launches_timed, clocks=clk.summary())
+    if gather_check is not None:
+        res["gather_check"] = gather_check
+    if world == 1 and not args.no_triton and args.scale == 1.0:
+        tb = triton_baseline(case, info, fast_step())
+        if "ms_per_step" in tb:
+            tb["value"] = tokens_all / (tb["ms_per_step"] * 1e-3)
+            tb["unit"] = "tokens/s"
+            res["speedup_vs_triton"] = tb["ms_per_step"] / eager_ms
+        res["triton_baseline"] = tb
+    return res
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the library has no CPU path)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    head = run_workload(args.workload, args, world, rank, local_rank, device)
+    torch.cuda.empty_cache()
+    also = {}
+    if not args.no_also and args.scale == 1.0 and args.workload == "c4" and args.kv_dtype == "auto":
+        for name in ["c5"] + (["c3"] if world == 1 else []):
+            r = run_workload(name, args, world, rank, local_rank, device)
+            torch.cuda.empty_cache()
+            also[name] = {k: r[k] for k in ("value", "unit", "ms_per_step", "tokens_per_step", "dtype", "config",
+                                            "execution", "roofline", "e2e", "gpu_launches", "gather_check",
+                                            "triton_baseline", "speedup_vs_triton") if k in r}
+
     if rank == 0:
-        line = dict(metric="deferred-RoPE attention throughput (query tokens/s per attention-layer call)",
-                    value=value, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
-                    ms_per_step=ms_per_step, higher_is_better=True, scaling=info["scaling"], vs_baseline=None,
-                    dtype="bf16" if info["kind"] == "prefill" and "fp8" not in args.kv_dtype else
-                    f"bf16 query, {case['kv_cache_dtype'].replace('auto', 'bf16').replace('fp8_', '')} KV, f32 accumulate",
-                    data="synthetic",
-                    config=dict(workload=info["workload"], variant=args.variant, kernel=args.kernel,
-                                partition=info["partition"], l2=info["l2"]),
-                    execution=dict(launch=launch_mode, gather=gather_mode),
-                    roofline=roof, e2e=e2e, gpu_launches=launches_timed, clocks=clk.summary())
+        line = dict(metric=METRIC, value=head["value"], unit="tokens/s", n_gpus=world, steps=args.steps,
+                    warmup=args.warmup, ms_per_step=head["ms_per_step"], higher_is_better=True,
+                    scaling=head["scaling"], vs_baseline=None, dtype=head["dtype"], data="synthetic",
+                    tokens_per_step=head["tokens_per_step"], config=head["config"], execution=head["execution"],
+                    roofline=head["roofline"], e2e=head["e2e"],
+                    gpu_launches=head["gpu_launches"] + sum(a["gpu_launches"] for a in also.values()),
+                    clocks=head["clocks"])
+        for k in ("gather_check", "triton_baseline", "speedup_vs_triton"):
+            if k in head:
+                line[k] = head[k]
+        if also:
+            line["also"] = also
         if not args.no_cpu_baseline and world == 1:
-            cb = cpu_baseline(args.workload, args.variant)
-            full_flops, full_units = full_workload_flops(args.workload)
-            tok_s = full_units / (cb["seconds_per_call"] * full_flops / cb["flops"])
-            line["cpu_baseline"] = dict(value=tok_s, unit="tokens/s", cores=cb["cores"], kind="port",
-                                        sample=cb["sample"] + "; rate scaled to the full call by FLOPs")
+            line["cpu_baseline"] = cpu_baseline(args.workload, args.variant)
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

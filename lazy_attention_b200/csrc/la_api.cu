@@ -17,10 +17,18 @@ void set_error(const char* fmt, ...) {
 
 __device__ int g_device_status[4];
 
+// Device address of the status word on the current device, looked up once per device.
 int* device_status_ptr() {
-  void* ptr = nullptr;
-  if (cudaGetSymbolAddress(&ptr, g_device_status) != cudaSuccess) return nullptr;
-  return reinterpret_cast<int*>(ptr);
+  constexpr int kMaxDevices = 64;
+  static std::atomic<int*> cached[kMaxDevices];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  int* ptr = cached[dev].load(std::memory_order_acquire);
+  if (ptr != nullptr) return ptr;
+  void* sym = nullptr;
+  if (cudaGetSymbolAddress(&sym, g_device_status) != cudaSuccess) return nullptr;
+  cached[dev].store(reinterpret_cast<int*>(sym), std::memory_order_release);
+  return reinterpret_cast<int*>(sym);
 }
 
 namespace {
@@ -122,11 +130,12 @@ extern "C" int la_prefill_fwd(const LaPrefillArgs* args, void* stream) {
     LA_REQUIRE(tc_ok, LA_ERR_UNSUPPORTED, "la_prefill_fwd: tensor-core kernel unavailable: %s", why);
     return launch_tc_prefill(*args, s);
   }
-  if (tc_ok && args->workspace_bytes >= tc_prefill_workspace_bytes(*args) &&
-      (args->workspace != nullptr || tc_prefill_workspace_bytes(*args) == 0))
-    return launch_tc_prefill(*args, s);
+  // Automatic selection: the tensor-core kernel whenever the arguments fit it.  A missing
+  // or short workspace is then an error of the call (launch_tc_prefill reports the size
+  // needed), never a reason to run the far slower general kernel unasked.
+  if (tc_ok) return launch_tc_prefill(*args, s);
   LA_REQUIRE(args->peer.num_peers == 0, LA_ERR_UNSUPPORTED,
-             "la_prefill_fwd: the fused output gather needs the tensor-core kernel (%s) and its workspace", why);
+             "la_prefill_fwd: the fused output gather needs the tensor-core kernel (%s)", why);
   return launch_general_prefill(*args, s);
 }
 
@@ -145,11 +154,10 @@ extern "C" int la_decode_fwd(const LaDecodeArgs* args, void* stream) {
     LA_REQUIRE(fast_ok, LA_ERR_UNSUPPORTED, "la_decode_fwd: split-KV kernel unavailable: %s", why);
     return launch_fast_decode(*args, s);
   }
-  if (fast_ok && args->workspace_bytes >= fast_decode_workspace_bytes(*args) &&
-      (args->workspace != nullptr || fast_decode_workspace_bytes(*args) == 0))
-    return launch_fast_decode(*args, s);
+  // As above: a missing or short workspace is reported, not papered over by the general kernel.
+  if (fast_ok) return launch_fast_decode(*args, s);
   LA_REQUIRE(args->peer.num_peers == 0, LA_ERR_UNSUPPORTED,
-             "la_decode_fwd: the fused output gather needs the split-KV kernel (%s) and its workspace", why);
+             "la_decode_fwd: the fused output gather needs the split-KV kernel (%s)", why);
   return launch_general_decode(*args, s);
 }
 

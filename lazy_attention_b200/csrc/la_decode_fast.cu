@@ -175,9 +175,12 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
   if (p.qsl[seq + 1] - row_q != 1) return;
   const int seq_len = p.seq_lens[seq];
   const int npages = (seq_len + 15) >> 4;
-  const int page0 = split * p.chunk_pages;
-  if (page0 >= npages) return;
-  const int n = min(p.chunk_pages, npages - page0);
+  const int first_page = split * p.chunk_pages;
+  if (first_page >= npages) return;
+  // The plan (chunk size, split count) comes from the caller's max_seq_len.  A
+  // sequence longer than that bound is still covered in full: the last split
+  // walks on, chunk by chunk, to the sequence's real last page.
+  const int end_page = (split == p.n_splits - 1) ? npages : min(npages, first_page + p.chunk_pages);
   const bool lazy = !MEPIC && p.is_lazy != nullptr && p.is_lazy[seq] != 0;
   const int64_t* prow = MEPIC ? nullptr : p.packed + (int64_t)seq * p.packed_stride;
 
@@ -185,56 +188,6 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
     for (int i = 0; i < W * S; ++i) mbar_init(&bar_full[i], 1);
     mbar_fence_init();
   }
-  // ---- page entries of this chunk: physical page, rotation in force, pad count.
-  // All threads fetch the packed entries; warp 0 then resolves "offset 0 keeps the
-  // rotation in force" with a scan, seeded by a backward search before the chunk.
-  for (int i = tid; i < n; i += Cfg::kThreads) {
-    if constexpr (MEPIC) {
-      int blk = p.block_table[(int64_t)seq * p.table_stride + page0 + i];
-      if (p.num_blocks > 0) blk = max(0, min(blk, (int)p.num_blocks - 1));
-      const int pad = min(max(p.q_mask[(int64_t)seq * p.table_stride + page0 + i], 0), 16);
-      ent[i] = make_int2(blk, (1 << 16) | pad);
-      continue;
-    }
-    const int64_t pk = prow[page0 + i];
-    int blk = (int)(pk >> 32);
-    if (p.num_blocks > 0) blk = max(0, min(blk, (int)p.num_blocks - 1));
-    const int rot = lazy ? (int)((pk >> 16) & 0xFFFF) : 1;
-    const int pad = (lazy && !p.ignore_q_mask) ? min((int)(pk & 0xFFFF), 16) : 0;
-    ent[i] = make_int2(blk, (rot << 16) | pad);
-  }
-  __syncthreads();
-  if (warp == 0 && lazy) {
-    int carry = 1;
-    if (page0 > 0) {
-      for (int base = page0 - 32;; base -= 32) {
-        const int idx = base + lane;
-        int rot = 0;
-        if (idx >= 0 && idx < page0) rot = (int)((prow[idx] >> 16) & 0xFFFF);
-        const unsigned m = __ballot_sync(0xffffffffu, rot != 0);
-        if (m) {
-          carry = __shfl_sync(0xffffffffu, rot, 31 - __clz(m));
-          break;
-        }
-        if (base <= 0) break;
-      }
-    }
-    for (int g0 = 0; g0 < n; g0 += 32) {
-      const int i = g0 + lane;
-      int2 e = make_int2(0, 0);
-      if (i < n) e = ent[i];
-      int eff = e.y >> 16;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int up = __shfl_up_sync(0xffffffffu, eff, o);
-        if (lane >= o && eff == 0) eff = up;
-      }
-      if (eff == 0) eff = carry;
-      carry = __shfl_sync(0xffffffffu, eff, 31);
-      if (i < n) ent[i] = make_int2(e.x, (eff << 16) | (e.y & 0xFFFF));
-    }
-  }
-
   // ---- Q fragments (B operand: head = lane/4, four consecutive dims per k-step)
   uint32_t qfull[KSTEPS][2], qcur[KSTEPS][2];
   {
@@ -291,15 +244,75 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
   const float v_scale = (KV != 0 && p.v_scale) ? *p.v_scale : 1.f;
   const float scale_log2 = p.sm_scale * k_scale * 1.4426950408889634f;
 
-  // ---- this warp's tiles: tile tl covers chunk pages 2*tl, 2*tl+1; warp w takes tl = w, w+W, ...
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[KSTEPS][4];
+#pragma unroll
+  for (int mt = 0; mt < KSTEPS; ++mt) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
+  const int tok_lo = sigma(r), tok_hi = tok_lo ^ 2;
+  bool ok = true;
+  int git = 0;  // tiles this warp has issued and consumed so far (ring stage and phase)
   constexpr int PPT = Cfg::kPPT;
-  const int n_tiles = (n + PPT - 1) / PPT;
-  const int my_tiles = n_tiles > warp ? (n_tiles - warp + W - 1) / W : 0;
   uint8_t* ring = smem + (size_t)warp * S * Cfg::kTileBytes;
   uint64_t* my_bar = bar_full + warp * S;
+
+  for (int page0 = first_page; page0 < end_page && ok; page0 += p.chunk_pages) {
+  const int n = min(p.chunk_pages, end_page - page0);
+  // ---- page entries of this chunk: physical page, rotation in force, pad count.
+  // All threads fetch the packed entries; warp 0 then resolves "offset 0 keeps the
+  // rotation in force" with a scan, seeded by a backward search before the chunk.
+  for (int i = tid; i < n; i += Cfg::kThreads) {
+    if constexpr (MEPIC) {
+      int blk = p.block_table[(int64_t)seq * p.table_stride + page0 + i];
+      if (p.num_blocks > 0) blk = max(0, min(blk, (int)p.num_blocks - 1));
+      const int pad = min(max(p.q_mask[(int64_t)seq * p.table_stride + page0 + i], 0), 16);
+      ent[i] = make_int2(blk, (1 << 16) | pad);
+      continue;
+    }
+    const int64_t pk = prow[page0 + i];
+    int blk = (int)(pk >> 32);
+    if (p.num_blocks > 0) blk = max(0, min(blk, (int)p.num_blocks - 1));
+    const int rot = lazy ? (int)((pk >> 16) & 0xFFFF) : 1;
+    const int pad = (lazy && !p.ignore_q_mask) ? min((int)(pk & 0xFFFF), 16) : 0;
+    ent[i] = make_int2(blk, (rot << 16) | pad);
+  }
+  __syncthreads();
+  if (warp == 0 && lazy) {
+    int carry = 1;
+    if (page0 > 0) {
+      for (int base = page0 - 32;; base -= 32) {
+        const int idx = base + lane;
+        int rot = 0;
+        if (idx >= 0 && idx < page0) rot = (int)((prow[idx] >> 16) & 0xFFFF);
+        const unsigned m = __ballot_sync(0xffffffffu, rot != 0);
+        if (m) {
+          carry = __shfl_sync(0xffffffffu, rot, 31 - __clz(m));
+          break;
+        }
+        if (base <= 0) break;
+      }
+    }
+    for (int g0 = 0; g0 < n; g0 += 32) {
+      const int i = g0 + lane;
+      int2 e = make_int2(0, 0);
+      if (i < n) e = ent[i];
+      int eff = e.y >> 16;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, eff, o);
+        if (lane >= o && eff == 0) eff = up;
+      }
+      if (eff == 0) eff = carry;
+      carry = __shfl_sync(0xffffffffu, eff, 31);
+      if (i < n) ent[i] = make_int2(e.x, (eff << 16) | (e.y & 0xFFFF));
+    }
+  }
+
+  // ---- this warp's tiles: tile tl covers chunk pages 2*tl, 2*tl+1; warp w takes tl = w, w+W, ...
+  const int n_tiles = (n + PPT - 1) / PPT;
+  const int my_tiles = n_tiles > warp ? (n_tiles - warp + W - 1) / W : 0;
   auto issue = [&](int it) {  // lane 0 only
     const int tl = warp + it * W;
-    const int st = it % S;
+    const int st = (git + it) % S;
     uint8_t* dst = ring + st * Cfg::kTileBytes;
     const int pg = PPT * tl;
     const int np = min(PPT, n - pg);
@@ -316,18 +329,11 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
     for (int it = 0; it < min(S, my_tiles); ++it) issue(it);
   __syncthreads();  // the rotation scan of warp 0 is complete
 
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  float o[KSTEPS][4];
-#pragma unroll
-  for (int mt = 0; mt < KSTEPS; ++mt) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
-  const int tok_lo = sigma(r), tok_hi = tok_lo ^ 2;
-  bool ok = true;
-
   for (int it = 0; it < my_tiles; ++it) {
     const int tl = warp + it * W;
-    const int st = it % S;
+    const int st = (git + it) % S;
     const uint8_t* tile = ring + st * Cfg::kTileBytes;
-    ok = mbar_wait(&my_bar[st], (uint32_t)(it / S) & 1u, p.status, 501);
+    ok = mbar_wait(&my_bar[st], (uint32_t)((git + it) / S) & 1u, p.status, 501);
     ok = __all_sync(0xffffffffu, ok) != 0;
     if (!ok) break;
     const int pg = PPT * tl;
@@ -496,6 +502,10 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
       issue(it + S);
     }
   }
+  git += my_tiles;
+  // every warp is done with this chunk's entries; a warp whose wait expired stops the whole CTA
+  ok = __syncthreads_and(ok) != 0;
+  }  // chunks of this split
 
   // ---- merge the warps of the CTA, then write the result or the split's partial
   __syncthreads();  // every warp has consumed all it issued: the ring can be reused

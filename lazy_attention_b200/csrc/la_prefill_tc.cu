@@ -6,17 +6,18 @@
 // first the cached pages (8 pages of 16 tokens per tile, gathered through the
 // block table by one TMA copy per page), then the new tokens (causal).
 //
-// Warp roles (22 warps):
-//   0-7   softmax of row tile 0: two threads per row, each owning 64 of the 128
-//         score columns (S/P/O live in tensor memory); they also stage the Q
-//         tiles at CTA start
-//   8-15  softmax of row tile 1
-//   16-19 operand staging: rotation of each landed K tile in shared memory by
+// Warp roles (14 warps):
+//   0-3   softmax of row tile 0: one thread per row, the row's 128 scores taken
+//         from tensor memory in four 32-column chunks (the next chunk is in
+//         flight while the current one is exponentiated); S/P/O live in tensor
+//         memory; these warps also stage the Q tiles at CTA start
+//   4-7   softmax of row tile 1
+//   8-11  operand staging: rotation of each landed K tile in shared memory by
 //         the page's (or token's) position; new-token K/V tiles; with an fp8
 //         cache also the copy and conversion of the raw pages
-//   20    MMA issue (one thread): S = Q K^T (operands in shared memory),
+//   12    MMA issue (one thread): S = Q K^T (operands in shared memory),
 //         O += P V (P read from tensor memory, V from shared memory)
-//   21    TMA issue: K and V pages into their stage rings
+//   13    TMA issue: K and V pages into their stage rings
 //
 // Shared-memory operand layout (no swizzle, K-major "core matrices" of
 // 8 rows x 16 bytes): the page layouts of the cache map onto it directly:
@@ -42,11 +43,26 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kThreadsTc = 22 * 32;
+constexpr int kThreadsTc = 14 * 32;
+constexpr int kSoftmaxThreads = 8 * 32;
+constexpr int kWarpStage = 8, kWarpMma = 12;  // first staging warp, MMA-issue warp (the TMA warp follows)
 constexpr int kRowsPerCta = 256;
 constexpr int kTileN = 128;
 constexpr int kPagesPerTile = 8;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
+
+// Optional timeline of CTA (0,0,0) for kernel tuning: compiled in only with -DLA_TRACE
+// (clock stamps per tile into a device array read back by la_trace_read).
+#ifdef LA_TRACE
+constexpr int kTraceRows = 32, kTraceCols = 256;
+__device__ long long g_trace[kTraceRows][kTraceCols];
+#define LA_STAMP(row, col)                                                                      \
+  do {                                                                                          \
+    if (trace_on && (col) >= 0 && (col) < kTraceCols) g_trace[(row)][(col)] = clock64();         \
+  } while (0)
+#else
+#define LA_STAMP(row, col) do { } while (0)
+#endif
 
 struct TcParams {
   const void* q;
@@ -85,6 +101,14 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
+// Same instruction without `volatile`: a pure function the compiler may schedule freely
+// (the branch-free exponential pass interleaves it with the packing of earlier values).
+__device__ __forceinline__ float ex2_pure(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -107,6 +131,40 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
       "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
+}
+
+// Waits for this thread's tensor-memory loads.  The loaded registers are passed through
+// the statement so that no use of them can be scheduled ahead of the wait.
+__device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+// Orders uses of `r` after the preceding wait (no instruction is emitted).
+__device__ __forceinline__ void tie_after_wait(uint32_t (&r)[32]) {
+  asm volatile(""
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+
+__device__ __forceinline__ float row_max32(const uint32_t (&sc)[32]) {
+  float mx0 = fmax3(__uint_as_float(sc[0]), __uint_as_float(sc[1]), __uint_as_float(sc[2]));
+  float mx1 = fmax3(__uint_as_float(sc[3]), __uint_as_float(sc[4]), __uint_as_float(sc[5]));
+#pragma unroll
+  for (int i = 6; i + 3 < 32; i += 4) {
+    mx0 = fmax3(mx0, __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]));
+    mx1 = fmax3(mx1, __uint_as_float(sc[i + 2]), __uint_as_float(sc[i + 3]));
+  }
+  mx0 = fmax3(mx0, __uint_as_float(sc[30]), __uint_as_float(sc[31]));
+  return fmaxf(mx0, mx1);
 }
 
 template <bool BF16>
@@ -258,13 +316,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
   uint8_t* sV = sK + KS * Cfg::kTileBytes;
   __shared__ __align__(8) uint64_t bar_k_tma[KS], bar_k_ready[KS], bar_k_empty[KS];
   __shared__ __align__(8) uint64_t bar_v_tma[KS], bar_v_ready[KS], bar_v_empty[KS];
-  __shared__ __align__(8) uint64_t bar_s_full[2], bar_p_full[2], bar_o_done, bar_q_ready, bar_xchg[2][4];
+  __shared__ __align__(8) uint64_t bar_s_full[2], bar_p_full[2], bar_o_done, bar_q_ready;
   __shared__ uint32_t tmem_base_s;
-  __shared__ unsigned long long xchg[2][128][4];  // per row: 2 alternating slots x 2 column halves
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int mb = blockIdx.x, kvh = blockIdx.y;
   const int b = blockIdx.z / p.n_splits, split = blockIdx.z % p.n_splits;
+#ifdef LA_TRACE
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp & 3) == 0;
+#endif
   const int s0 = p.qsl[b];
   const int qlen = p.qsl[b + 1] - s0;
   if (qlen <= 0 || (p.skip_decode && qlen == 1)) return;
@@ -296,15 +356,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
     }
     mbar_init(&bar_s_full[0], 1);
     mbar_init(&bar_s_full[1], 1);
-    mbar_init(&bar_p_full[0], 256);
-    mbar_init(&bar_p_full[1], 256);
+    mbar_init(&bar_p_full[0], 128);
+    mbar_init(&bar_p_full[1], 128);
     mbar_init(&bar_o_done, 1);
-    mbar_init(&bar_q_ready, 512);
-    for (int i = 0; i < 8; ++i) mbar_init(&bar_xchg[0][0] + i, 64);
+    mbar_init(&bar_q_ready, kSoftmaxThreads);
     mbar_fence_init();
   }
-  for (int i = tid; i < 2 * 128 * 4; i += kThreadsTc) (&xchg[0][0][0])[i] = 0ull;
-  if (warp == 20) {
+  if (warp == kWarpMma) {
     tmem_alloc(&tmem_base_s, 512);
     tmem_relinquish();
   }
@@ -318,13 +376,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
   const float scale_log2_ctx = p.scale_log2 * ((KVF8 != 0 && p.k_scale) ? *p.k_scale : 1.f);
   const float out_scale = (KVF8 != 0 && p.v_scale) ? *p.v_scale : 1.f;
 
-  if (warp < 16) {
+  if (warp < kWarpStage) {
     // =============================== softmax ===============================
-    // Two threads per row: thread (row, hf) owns the 32-column chunks hf and hf+2 of
-    // the row's 128 scores.  The pair agrees on the running maximum chunk by chunk
-    // through shared memory and an mbarrier of the two warps (bounded wait).
-    const int t = warp >> 3;          // row tile
-    const int hf = (warp >> 2) & 1;   // column half
+    // One thread per score row.  The row's 128 scores of a tile are consumed in four
+    // 32-column chunks: while chunk c is scaled, exponentiated and packed, the
+    // tensor-memory load of chunk c+1 is already in flight.  P (two keys per column)
+    // is written over S columns 0..63, always behind the columns still to be read.
+    const int t = warp >> 2;          // row tile
     const int qd = warp & 3;          // lane quarter of tensor memory this warp may touch
     const int r = qd * 32 + lane;     // row within the tile
     const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
@@ -332,28 +390,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
     const uint32_t tO = tmem + 256 + t * 128 + lane_addr;
     const int R = row0 + t * 128 + r;
     const int tq = R >> p.g_shift;
-    // Exchange of one float with the partner thread of the row: both warps of a
-    // (row tile, lane quarter) post their values in shared memory and meet on an
-    // mbarrier of 64 arrivals; the wait suspends in hardware, so the warp that is
-    // ahead takes no issue slots from its partner (both run on the same scheduler).
-    // Slots alternate with the sequence parity: a slot is rewritten only after the
-    // barrier phase that follows its reads.  The wait is bounded like every other.
-    volatile float* xrow = reinterpret_cast<volatile float*>(&xchg[t][r][0]);
-    uint64_t* xbar = &bar_xchg[t][qd];
-    auto pair_exchange = [&](float v, uint32_t seq, bool& good) -> float {
-      const int base = (seq & 1u) * 2;
-      xrow[base + hf] = v;
-      mbar_arrive(xbar);
-      if (!mbar_wait(xbar, (seq - 1u) & 1u, p.status, 131)) { good = false; return v; }
-      return xrow[base + (hf ^ 1)];
-    };
     // ---- Q tiles: rows R = row0 .. row0+255, chunk-coalesced global reads.  The softmax
     // warps have nothing to do until the first scores exist, so they stage Q while the
     // staging warps already work on the first K tile.
     {
       const uint8_t* qb = reinterpret_cast<const uint8_t*>(p.q);
 #pragma unroll 4
-      for (int idx = tid; idx < kRowsPerCta * NCH; idx += 512) {
+      for (int idx = tid; idx < kRowsPerCta * NCH; idx += kSoftmaxThreads) {
         const int row = idx / NCH, g = idx - row * NCH;
         const int Rq = row0 + row;
         const int tqq = Rq >> p.g_shift;
@@ -385,6 +428,98 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
       }
       return v;
     };
+    // One 32-column chunk: mask, row maximum, lazy rescale, exponentials, P.
+    auto do_chunk = [&](uint32_t (&sc)[32], const int c, const int j, const bool self, const bool tile_full,
+                        const int vc, const int n0, const float scale_log2) {
+      const int col0 = c * 32;
+      if (self) {
+        const int lim = tq - (n0 + col0);  // columns 0..lim are visible
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i > lim) sc[i] = 0xff800000u;
+      } else if (!tile_full) {
+        const int va = __shfl_sync(0xffffffffu, vc, 2 * c), vb = __shfl_sync(0xffffffffu, vc, 2 * c + 1);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          if (i >= va) sc[i] = 0xff800000u;
+          if (i >= vb) sc[16 + i] = 0xff800000u;
+        }
+      }
+      float mx0 = fmax3(__uint_as_float(sc[0]), __uint_as_float(sc[1]), __uint_as_float(sc[2]));
+      float mx1 = fmax3(__uint_as_float(sc[3]), __uint_as_float(sc[4]), __uint_as_float(sc[5]));
+#pragma unroll
+      for (int i = 6; i + 3 < 32; i += 4) {
+        mx0 = fmax3(mx0, __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(sc[i + 2]), __uint_as_float(sc[i + 3]));
+      }
+      mx0 = fmax3(mx0, __uint_as_float(sc[30]), __uint_as_float(sc[31]));
+      const float m_chunk = fmaxf(mx0, mx1) * scale_log2;
+      float alpha = 1.f;
+      if (j == j0 && c == 0) {
+        m_used = m_chunk;
+      } else if (m_chunk > m_used + kRescaleThreshold) {
+        alpha = ex2f(m_used - m_chunk);  // m_used == -inf gives 0
+        m_used = m_chunk;
+      }
+      if (__any_sync(0xffffffffu, alpha != 1.f)) {
+        // Rare (the running maximum grew by more than the threshold): bring what was
+        // accumulated under the old maximum to the new one.  Tensor-memory accesses
+        // are warp-collective, so the whole warp takes this path together.
+        l_sum *= alpha;
+        if (j != j0) {
+#pragma unroll 1
+          for (int oc = 0; oc < D / 32; ++oc) {
+            uint32_t o[32];
+            tmem_ld32(tO + oc * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tO + oc * 32, o);
+          }
+        }
+#pragma unroll 1
+        for (int pc = 0; pc < c; ++pc) {  // P chunks of this tile formed with the old maximum
+          uint32_t pp[16];
+          tmem_ld16(tS + pc * 16, pp);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float2 f = unpack2<MB>(pp[i]);
+            pp[i] = pack2<MB>(f.x * alpha, f.y * alpha);
+          }
+          tmem_st16(tS + pc * 16, pp);
+        }
+        tmem_st_wait();
+      }
+      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+      const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(neg_m, neg_m);
+      uint32_t pk[16];
+      float2 acc_a = make_float2(0.f, 0.f), acc_b = make_float2(0.f, 0.f);
+      // three passes over the registers: arguments, exponentials (the 32 MUFU
+      // operations back to back), then sums and packing
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const float2 x = __ffma2_rn(make_float2(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1])), sc2, nm2);
+        sc[i] = __float_as_uint(x.x);
+        sc[i + 1] = __float_as_uint(x.y);
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) sc[i] = __float_as_uint(ex2f(__uint_as_float(sc[i])));
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const float2 e = make_float2(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1]));
+        if (i & 2) acc_b = __fadd2_rn(acc_b, e); else acc_a = __fadd2_rn(acc_a, e);
+        if constexpr (MB) {
+          const uint32_t b0 = sc[i] + 0x8000u;  // round-half-up, then keep the high halves
+          const uint32_t b1 = sc[i + 1] + 0x8000u;
+          pk[i >> 1] = __byte_perm(b0, b1, 0x7632);
+        } else {
+          pk[i >> 1] = pack2<false>(e.x, e.y);
+        }
+      }
+      l_sum += (acc_a.x + acc_a.y) + (acc_b.x + acc_b.y);
+      tmem_st16(tS + c * 16, pk);
+    };
     int vc_next = page_valid(j0);
     for (int j = j0; j < j1 && ok; ++j) {
       const bool self = j >= n_ctx;
@@ -396,132 +531,146 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
       ok = mbar_wait(&bar_s_full[t], (uint32_t)(j - j0) & 1u, p.status, 101 + t);
       if (!ok) break;
       tc_fence_after_sync();
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        // chunk of this thread: keys [64c + 32hf, +32).  P (two keys per column) is
-        // written over S columns 0..63, i.e. over the first chunks of both threads;
-        // the maximum exchange orders those writes after both first chunks were read.
-        const int col0 = c * 64 + hf * 32;
-        uint32_t sc[32];
-        tmem_ld32(tS + col0, sc);
-        tmem_ld_wait();
-        if (self) {
-          const int lim = tq - (n0 + col0);  // columns 0..lim are visible
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (i > lim) sc[i] = 0xff800000u;
-        } else if (!tile_full) {
-          const int va = __shfl_sync(0xffffffffu, vc, col0 >> 4), vb = __shfl_sync(0xffffffffu, vc, (col0 >> 4) + 1);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            if (i >= va) sc[i] = 0xff800000u;
-            if (i >= vb) sc[16 + i] = 0xff800000u;
-          }
-        }
-        float mx0 = fmax3(__uint_as_float(sc[0]), __uint_as_float(sc[1]), __uint_as_float(sc[2]));
-        float mx1 = fmax3(__uint_as_float(sc[3]), __uint_as_float(sc[4]), __uint_as_float(sc[5]));
-#pragma unroll
-        for (int i = 6; i + 3 < 32; i += 4) {
-          mx0 = fmax3(mx0, __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]));
-          mx1 = fmax3(mx1, __uint_as_float(sc[i + 2]), __uint_as_float(sc[i + 3]));
-        }
-        mx0 = fmax3(mx0, __uint_as_float(sc[30]), __uint_as_float(sc[31]));
-        // agree with the partner thread of this row on the chunk maximum
-        const float mx_mine = fmaxf(mx0, mx1);
-        const float mx_other = pair_exchange(mx_mine, (uint32_t)(2 * (j - j0) + c + 1), ok);
-        const float m_chunk = fmaxf(mx_mine, mx_other) * scale_log2;
+      LA_STAMP(t * 8 + 0, j - j0);
+      uint32_t sa[32], sb[32];
+      if (tile_full) {
+        // ---- fast path (every key of the tile is visible): two passes over the row.
+        // Pass A: the row maximum of the whole tile, so that the one decision about the
+        // running maximum is taken before any exponential is formed.
+        tmem_ld32(tS, sa);
+        tmem_ld32(tS + 32, sb);
+        tmem_ld_wait_for(sa);
+        tie_after_wait(sb);
+        float mx_a = row_max32(sa), mx_b = row_max32(sb);
+        tmem_ld32(tS + 64, sa);
+        tmem_ld32(tS + 96, sb);
+        tmem_ld_wait_for(sa);
+        tie_after_wait(sb);
+        mx_a = fmaxf(mx_a, row_max32(sa));
+        mx_b = fmaxf(mx_b, row_max32(sb));
+        const float m_tile = fmaxf(mx_a, mx_b) * scale_log2;
+        // the first two chunks are fetched again while the decision is taken
+        tmem_ld32(tS, sa);
+        tmem_ld32(tS + 32, sb);
+        LA_STAMP(t * 8 + 1, j - j0);
         float alpha = 1.f;
-        if (j == j0 && c == 0) {
-          m_used = m_chunk;
-        } else if (m_chunk > m_used + kRescaleThreshold) {
-          alpha = ex2f(m_used - m_chunk);  // m_used == -inf gives 0
-          m_used = m_chunk;
+        if (j == j0) {
+          m_used = m_tile;
+        } else if (m_tile > m_used + kRescaleThreshold) {
+          alpha = ex2f(m_used - m_tile);  // m_used == -inf gives 0
+          m_used = m_tile;
         }
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
-          // rare: the partner warp takes the same branch (same rows, same maxima)
+          // rare: bring the accumulator row and the row sum to the new maximum
           l_sum *= alpha;
           if (j != j0) {
+            tmem_ld_wait();
 #pragma unroll 1
-            for (int oc = 0; oc < D / 64; ++oc) {  // this thread's half of the accumulator row
+            for (int oc = 0; oc < D / 32; ++oc) {
               uint32_t o[32];
-              tmem_ld32(tO + hf * (D / 2) + oc * 32, o);
+              tmem_ld32(tO + oc * 32, o);
               tmem_ld_wait();
 #pragma unroll
               for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st32(tO + hf * (D / 2) + oc * 32, o);
+              tmem_st32(tO + oc * 32, o);
             }
+            tmem_st_wait();
+            tmem_ld32(tS, sa);
+            tmem_ld32(tS + 32, sb);
           }
-          if (c == 1) {  // this thread's first P chunk was formed with the old maximum
-            uint32_t pp[16];
-            tmem_ld16(tS + hf * 16, pp);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float2 f = unpack2<MB>(pp[i]);
-              pp[i] = pack2<MB>(f.x * alpha, f.y * alpha);
-            }
-            tmem_st16(tS + hf * 16, pp);
-          }
-          tmem_st_wait();
         }
-        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+        // Pass B: exponentials and P, one straight-line block for the four chunks.
+        // bf16 P is formed by truncation of e * (1 + 2^-9) (the factor rides on the
+        // subtracted maximum), which is unbiased like rounding and costs one byte
+        // permute per pair instead of two integer adds and a permute; the row sum is
+        // taken from the same values and scaled back by 1 / (1 + 2^-9).
+        constexpr float kBiasLog2 = MB ? 0.0028151247f : 0.f;       // log2(1 + 2^-9)
+        constexpr float kUnbias = MB ? 0.998050682f : 1.f;          // 1 / (1 + 2^-9)
+        const float neg_m = ((m_used == -INFINITY) ? 0.f : -m_used) + kBiasLog2;
         const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(neg_m, neg_m);
-        uint32_t pk[16];
         float2 acc_a = make_float2(0.f, 0.f), acc_b = make_float2(0.f, 0.f);
-        // three passes over the registers: arguments, exponentials (the 32 MUFU
-        // operations back to back), then sums and packing
+        auto exp_chunk = [&](uint32_t (&sc)[32], const int c) {
+          uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float2 x = __ffma2_rn(make_float2(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1])), sc2, nm2);
-          sc[i] = __float_as_uint(x.x);
-          sc[i + 1] = __float_as_uint(x.y);
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) sc[i] = __float_as_uint(ex2f(__uint_as_float(sc[i])));
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float2 e = make_float2(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1]));
-          if (i & 2) acc_b = __fadd2_rn(acc_b, e); else acc_a = __fadd2_rn(acc_a, e);
-          if constexpr (MB) {
-            const uint32_t b0 = sc[i] + 0x8000u;  // round-half-up, then keep the high halves
-            const uint32_t b1 = sc[i + 1] + 0x8000u;
-            pk[i >> 1] = __byte_perm(b0, b1, 0x7632);
-          } else {
-            pk[i >> 1] = pack2<false>(e.x, e.y);
+          for (int i = 0; i < 32; i += 2) {
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1])), sc2, nm2);
+            const float2 e = make_float2(ex2_pure(x.x), ex2_pure(x.y));
+            if (i & 2) acc_b = __fadd2_rn(acc_b, e); else acc_a = __fadd2_rn(acc_a, e);
+            if constexpr (MB) {
+              pk[i >> 1] = __byte_perm(__float_as_uint(e.x), __float_as_uint(e.y), 0x7632);
+            } else {
+              pk[i >> 1] = pack2<false>(e.x, e.y);
+            }
           }
-        }
-        l_sum += (acc_a.x + acc_a.y) + (acc_b.x + acc_b.y);
-        tmem_st16(tS + c * 32 + hf * 16, pk);
+          tmem_st16(tS + c * 16, pk);
+        };
+        tmem_ld_wait_for(sa);
+        tie_after_wait(sb);
+        exp_chunk(sa, 0);
+        tmem_ld32(tS + 64, sa);
+        LA_STAMP(t * 8 + 2, j - j0);
+        exp_chunk(sb, 1);
+        tmem_ld_wait_for(sa);
+        tmem_ld32(tS + 96, sb);
+        LA_STAMP(t * 8 + 3, j - j0);
+        exp_chunk(sa, 2);
+        tmem_ld_wait_for(sb);
+        LA_STAMP(t * 8 + 4, j - j0);
+        exp_chunk(sb, 3);
+        LA_STAMP(t * 8 + 5, j - j0);
+        l_sum = fmaf((acc_a.x + acc_a.y) + (acc_b.x + acc_b.y), kUnbias, l_sum);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        mbar_arrive(&bar_p_full[t]);
+        LA_STAMP(t * 8 + 6, j - j0);
+        continue;
       }
+      // ---- tiles with masked keys (ragged pages, causal new-token tiles): chunk by chunk
+      tmem_ld32(tS, sa);
+      tmem_ld_wait();
+      LA_STAMP(t * 8 + 1, j - j0);
+      tmem_ld32(tS + 32, sb);
+      do_chunk(sa, 0, j, self, tile_full, vc, n0, scale_log2);
+      LA_STAMP(t * 8 + 2, j - j0);
+      tmem_ld_wait();
+      tmem_ld32(tS + 64, sa);
+      do_chunk(sb, 1, j, self, tile_full, vc, n0, scale_log2);
+      LA_STAMP(t * 8 + 3, j - j0);
+      tmem_ld_wait();
+      tmem_ld32(tS + 96, sb);
+      do_chunk(sa, 2, j, self, tile_full, vc, n0, scale_log2);
+      LA_STAMP(t * 8 + 4, j - j0);
+      tmem_ld_wait();
+      do_chunk(sb, 3, j, self, tile_full, vc, n0, scale_log2);
+      LA_STAMP(t * 8 + 5, j - j0);
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bar_p_full[t]);
+      LA_STAMP(t * 8 + 6, j - j0);
     }
-    // ---- epilogue: each thread writes its half of the head dimension
+    // ---- epilogue: each thread writes its row
     if (ok && ntiles > 0) ok = mbar_wait(&bar_o_done, 0, p.status, 111 + t);
     tc_fence_after_sync();
-    // total row sum = this thread's part + the partner's
-    const float l_row = l_sum + pair_exchange(l_sum, (uint32_t)(2 * ntiles + 1), ok);
+    const float l_row = l_sum;
     // Tensor-memory loads are warp-collective: every lane of the warp runs them,
     // rows past the request's last token only skip the global stores.
     const bool ok_warp = __all_sync(0xffffffffu, ok) != 0;
     if (ok_warp) {
       const bool row_valid = tq < qlen;
       const int head = kvh * G + (R & (G - 1));
-      constexpr int DH = D / 2;
       if (p.n_splits == 1) {
         const float inv = l_row > 0.f ? out_scale / l_row : 0.f;
         uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
-                        ((int64_t)(s0 + tq) * p.o_st + (int64_t)head * p.o_sh + hf * DH) * 2;
-        int64_t peer_off = 0;  // byte offset of this thread's half row in every rank's buffer
+                        ((int64_t)(s0 + tq) * p.o_st + (int64_t)head * p.o_sh) * 2;
+        int64_t peer_off = 0;  // byte offset of this thread's row in every rank's buffer
         if (p.peer.num_peers > 0 && row_valid) {
           const int64_t prow = p.peer.rows ? p.peer.rows[s0 + tq] : (s0 + tq);
-          peer_off = (prow * p.peer.stride_t + (int64_t)(p.peer.head_offset + head) * p.peer.stride_h + hf * DH) * 2;
+          peer_off = (prow * p.peer.stride_t + (int64_t)(p.peer.head_offset + head) * p.peer.stride_h) * 2;
         }
 #pragma unroll 1
-        for (int ch = 0; ch < DH / 32; ++ch) {
+        for (int ch = 0; ch < D / 32; ++ch) {
           uint32_t o[32];
-          tmem_ld32(tO + hf * DH + ch * 32, o);
+          tmem_ld32(tO + ch * 32, o);
           tmem_ld_wait();
           uint4 w[4];
           uint32_t* pw = reinterpret_cast<uint32_t*>(w);
@@ -543,12 +692,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
         }
       } else {
         const int64_t slot = (((int64_t)b * p.Hkv + kvh) * p.rows_cap + R) * p.n_splits + split;
-        float* po = p.part_o + slot * D + hf * DH;
+        float* po = p.part_o + slot * D;
         if (ntiles > 0) {
 #pragma unroll 1
-          for (int ch = 0; ch < DH / 32; ++ch) {
+          for (int ch = 0; ch < D / 32; ++ch) {
             uint32_t o[32];
-            tmem_ld32(tO + hf * DH + ch * 32, o);
+            tmem_ld32(tO + ch * 32, o);
             tmem_ld_wait();
             if (row_valid) {
 #pragma unroll
@@ -559,15 +708,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
             }
           }
         }
-        if (row_valid && hf == 0) {
+        if (row_valid) {
           p.part_ml[slot * 2] = ntiles > 0 ? m_used : -INFINITY;
           p.part_ml[slot * 2 + 1] = ntiles > 0 ? l_row : 0.f;
         }
       }
     }
-  } else if (warp < 20) {
+  } else if (warp < kWarpMma) {
     // =============================== operand staging ===============================
-    const int i = tid - 512;  // 0..127
+    const int i = tid - kWarpStage * 32;  // 0..127
     bool ok = true;
     const uint8_t* cs = reinterpret_cast<const uint8_t*>(p.cs);
     // fp8 caches: asynchronous copies of tile jn's raw pages into its operand stage
@@ -717,6 +866,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
         }
         ok = mbar_wait(&bar_k_tma[st], (uint32_t)u & 1u, p.status, 201);
         if (!ok) break;
+        LA_STAMP(21, j - j0);
         if (pos > 0) {
           uint8_t* rowp = kst + (i >> 3) * Cfg::kRowGroupBytes + (i & 7) * 16;
           uint4 cpost[NPRE], spost[NPRE];
@@ -736,6 +886,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
         }
         fence_proxy_async_smem();
         mbar_arrive(&bar_k_ready[st]);
+        LA_STAMP(20, j - j0);
       } else {
         // new tokens: K rows into the operand layout (rotated in per-token mode), V transposed
         if (u > 0) ok = mbar_wait(&bar_k_empty[st], (uint32_t)(u - 1) & 1u, p.status, 202);
@@ -797,7 +948,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
         mbar_arrive(&bar_v_ready[st]);
       }
     }
-  } else if (warp == 20) {
+  } else if (warp == kWarpMma) {
     // =============================== MMA issue ===============================
     if (ntiles > 0) {
       const bool issuer = lane == 0;
@@ -849,6 +1000,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
         ok = mbar_wait(&bar_p_full[0], (uint32_t)(j - j0) & 1u, p.status, 305);
         if (!ok) break;
         tc_fence_after_sync();
+        LA_STAMP(16, j - j0);
         issue_pv(0, st, npages, j == j0);
         if (has_next) {
           ok = mbar_wait(&bar_k_ready[st_n], (uint32_t)u_n & 1u, p.status, 306);
@@ -856,15 +1008,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
           tc_fence_after_sync();
           issue_qk(0, st_n);
         }
+        LA_STAMP(17, j - j0);
         ok = mbar_wait(&bar_p_full[1], (uint32_t)(j - j0) & 1u, p.status, 307);
         if (!ok) break;
         tc_fence_after_sync();
+        LA_STAMP(18, j - j0);
         issue_pv(1, st, npages, j == j0);
         if (issuer) mma_commit(&bar_v_empty[st]);
         if (has_next) {
           issue_qk(1, st_n);
           if (issuer) mma_commit(&bar_k_empty[st_n]);
         }
+        LA_STAMP(19, j - j0);
         __syncwarp();
       }
       if (ok && issuer) mma_commit(&bar_o_done);
@@ -897,7 +1052,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
   // ---- teardown: every role is done (or has given up); release tensor memory
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 20) tmem_dealloc(tmem, 512);
+  if (warp == kWarpMma) tmem_dealloc(tmem, 512);
 }
 
 // Merge the per-split partial results: out = sum_s 2^(m_s - m*) O_s / sum_s 2^(m_s - m*) l_s.
@@ -964,15 +1119,9 @@ struct MapPair {
 std::mutex g_map_mu;
 std::unordered_map<MapKey, MapPair, MapKeyHash> g_maps;
 
-int get_maps(const LaPrefillArgs& a, MapPair* out) {
-  MapKey key{a.k_cache, a.v_cache, a.num_blocks, a.kc_stride_block, a.kc_stride_head,
-             a.vc_stride_block, a.vc_stride_head, a.head_dim, a.q_dtype};
-  std::lock_guard<std::mutex> lock(g_map_mu);
-  auto it = g_maps.find(key);
-  if (it != g_maps.end()) {
-    *out = it->second;
-    return LA_OK;
-  }
+// The two tensor maps of a 16-bit cache: one page of one head per box, laid out
+// for the no-swizzle operand layout (see the head of this file).
+int encode_maps(const LaPrefillArgs& a, MapPair* mp) {
   EncodeTiledFn enc = get_encode_tiled();
   LA_REQUIRE(enc != nullptr, LA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const int D = a.head_dim;
@@ -980,14 +1129,13 @@ int get_maps(const LaPrefillArgs& a, MapPair* out) {
   const CUtensorMapDataType dt =
       a.q_dtype == LA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   cuuint32_t es[5] = {1, 1, 1, 1, 1};
-  MapPair mp;
   {
     // K page of one head: [D/8][16 tokens][8 elements]; dims innermost first:
     // 8 elements, 8 tokens, D/8 groups, 2 token halves, (page, head)
     cuuint64_t dim[5] = {8, 8, (cuuint64_t)D / 8, 2, n_idx};
     cuuint64_t str[4] = {16, 256, 128, (cuuint64_t)a.kc_stride_head * 2};
     cuuint32_t box[5] = {8, 8, (cuuint32_t)D / 8, 2, 1};
-    CUresult r = enc(&mp.k, dt, 5, const_cast<void*>(a.k_cache), dim, str, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    CUresult r = enc(&mp->k, dt, 5, const_cast<void*>(a.k_cache), dim, str, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     LA_REQUIRE(r == CUDA_SUCCESS, LA_ERR_CUDA, "cuTensorMapEncodeTiled(K cache) failed with %d", (int)r);
@@ -998,14 +1146,42 @@ int get_maps(const LaPrefillArgs& a, MapPair* out) {
     cuuint64_t dim[5] = {8, 8, 2, (cuuint64_t)D / 8, n_idx};
     cuuint64_t str[4] = {32, 16, 256, (cuuint64_t)a.vc_stride_head * 2};
     cuuint32_t box[5] = {8, 8, 2, (cuuint32_t)D / 8, 1};
-    CUresult r = enc(&mp.v, dt, 5, const_cast<void*>(a.v_cache), dim, str, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    CUresult r = enc(&mp->v, dt, 5, const_cast<void*>(a.v_cache), dim, str, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     LA_REQUIRE(r == CUDA_SUCCESS, LA_ERR_CUDA, "cuTensorMapEncodeTiled(V cache) failed with %d", (int)r);
   }
-  if (g_maps.size() > 4096) g_maps.clear();
-  g_maps.emplace(key, mp);
-  *out = mp;
+  return LA_OK;
+}
+
+// Tensor maps of a cache, remembered per (pointers, shape).  A layer is called again and
+// again with the same caches: the calling thread's last pair is checked first, without
+// taking the lock of the shared table.
+int cached_maps(const LaPrefillArgs& a, MapPair* out) {
+  MapKey key{a.k_cache, a.v_cache, a.num_blocks, a.kc_stride_block, a.kc_stride_head,
+             a.vc_stride_block, a.vc_stride_head, a.head_dim, a.q_dtype};
+  thread_local MapKey last_key{};
+  thread_local MapPair last_pair;
+  thread_local bool have_last = false;
+  if (have_last && last_key == key) {
+    *out = last_pair;
+    return LA_OK;
+  }
+  {
+    std::lock_guard<std::mutex> lock(g_map_mu);
+    auto it = g_maps.find(key);
+    if (it == g_maps.end()) {
+      MapPair mp;
+      int rc = encode_maps(a, &mp);
+      if (rc != LA_OK) return rc;
+      if (g_maps.size() > 4096) g_maps.clear();
+      it = g_maps.emplace(key, mp).first;
+    }
+    *out = it->second;
+  }
+  last_key = key;
+  last_pair = *out;
+  have_last = true;
   return LA_OK;
 }
 
@@ -1018,6 +1194,7 @@ int ilog2(int v) {
 struct TcPlan {
   int mblocks, n_splits;
   int64_t rows_cap;
+  size_t scratch_bytes;  // split-KV partials (0 when the KV range is not split)
 };
 
 TcPlan make_plan(const LaPrefillArgs& a) {
@@ -1048,6 +1225,11 @@ TcPlan make_plan(const LaPrefillArgs& a) {
     const int v = atoi(e);
     if (v >= 1 && v <= 16) pl.n_splits = v;
   }
+  pl.scratch_bytes = 0;
+  if (pl.n_splits > 1) {
+    const size_t slots = (size_t)a.batch * a.num_kv_heads * pl.rows_cap * pl.n_splits;
+    pl.scratch_bytes = slots * (a.head_dim + 2) * sizeof(float) + 256;
+  }
   return pl;
 }
 
@@ -1077,12 +1259,9 @@ bool tc_prefill_supported(const LaPrefillArgs& a, const char** why) {
   return true;
 }
 
-size_t tc_prefill_workspace_bytes(const LaPrefillArgs& a) {
-  const TcPlan pl = make_plan(a);
-  if (pl.n_splits <= 1) return 0;
-  const size_t slots = (size_t)a.batch * a.num_kv_heads * pl.rows_cap * pl.n_splits;
-  return slots * (a.head_dim + 2) * sizeof(float) + 256;
-}
+size_t tc_prefill_workspace_bytes(const LaPrefillArgs& a) { return make_plan(a).scratch_bytes; }
+
+namespace {
 
 template <int D, bool BF16, int KVF8>
 int launch_tc_kv(const LaPrefillArgs& a, const TcParams& p, const MapPair& mp, const TcPlan& pl,
@@ -1118,25 +1297,33 @@ int launch_tc(const LaPrefillArgs& a, const TcParams& p, const MapPair& mp, cons
   return launch_tc_kv<D, BF16, 0>(a, p, mp, pl, stream);
 }
 
-// Tensor maps cover 16-bit caches; fp8 caches are read with plain loads.
-int cache_access(const LaPrefillArgs& a, TcParams& p, MapPair* mp) {
-  std::memset(mp, 0, sizeof(*mp));
-  if (a.kv_dtype == a.q_dtype) return get_maps(a, mp);
-  p.kc = reinterpret_cast<const uint8_t*>(a.k_cache);
-  p.vc = reinterpret_cast<const uint8_t*>(a.v_cache);
-  p.kc_sb = a.kc_stride_block; p.kc_sh = a.kc_stride_head;
-  p.vc_sb = a.vc_stride_block; p.vc_sh = a.vc_stride_head;
-  p.num_blocks = a.num_blocks;
-  p.k_scale = a.k_scale; p.v_scale = a.v_scale;
-  return LA_OK;
-}
-
-int launch_tc_prefill(const LaPrefillArgs& a, cudaStream_t stream) {
+// The one launch path of the tensor-core kernel.  `scratch` holds the split-KV partials
+// (the caller's workspace, or the library's built-in array for the allocation-free entry
+// point); `keep_maps` says whether the tensor maps may be remembered between calls.
+int launch_tc_with_scratch(const LaPrefillArgs& a, cudaStream_t stream, void* scratch, size_t scratch_bytes,
+                           bool keep_maps, const char* who) {
+  const TcPlan pl = make_plan(a);
+  // The scratch is checked before anything touches the device, so that a caller who
+  // forgot the workspace learns the size from the error text.
+  LA_REQUIRE(pl.scratch_bytes == 0 || (scratch != nullptr && scratch_bytes >= pl.scratch_bytes), LA_ERR_WORKSPACE,
+             "%s: this call splits the KV range %d ways and needs %zu bytes of scratch, %zu were given", who,
+             pl.n_splits, pl.scratch_bytes, scratch ? scratch_bytes : (size_t)0);
   MapPair mp;
   TcParams p{};
-  int rc = cache_access(a, p, &mp);
-  if (rc != LA_OK) return rc;
-  const TcPlan pl = make_plan(a);
+  std::memset(&mp, 0, sizeof(mp));
+  if (a.kv_dtype == a.q_dtype) {
+    // 16-bit caches are read through tensor maps
+    int rc = keep_maps ? cached_maps(a, &mp) : encode_maps(a, &mp);
+    if (rc != LA_OK) return rc;
+  } else {
+    // fp8 caches are read with plain loads by the staging warps
+    p.kc = reinterpret_cast<const uint8_t*>(a.k_cache);
+    p.vc = reinterpret_cast<const uint8_t*>(a.v_cache);
+    p.kc_sb = a.kc_stride_block; p.kc_sh = a.kc_stride_head;
+    p.vc_sb = a.vc_stride_block; p.vc_sh = a.vc_stride_head;
+    p.num_blocks = a.num_blocks;
+    p.k_scale = a.k_scale; p.v_scale = a.v_scale;
+  }
   p.q = a.q; p.k = a.k; p.v = a.v; p.out = a.out;
   p.q_st = a.q_stride_t; p.q_sh = a.q_stride_h;
   p.k_st = a.k_stride_t; p.k_sh = a.k_stride_h;
@@ -1155,18 +1342,24 @@ int launch_tc_prefill(const LaPrefillArgs& a, cudaStream_t stream) {
   p.peer = a.peer;
   p.rows_cap = pl.rows_cap;
   if (pl.n_splits > 1) {
+    // Every slot the merge kernel reads is written by the attention kernel of the same
+    // call (empty splits write a neutral entry): the scratch never needs clearing.
     const size_t slots = (size_t)a.batch * a.num_kv_heads * pl.rows_cap * pl.n_splits;
-    LA_REQUIRE(a.workspace != nullptr && a.workspace_bytes >= tc_prefill_workspace_bytes(a), LA_ERR_WORKSPACE,
-               "la_prefill_fwd: split-KV needs %zu bytes of workspace", tc_prefill_workspace_bytes(a));
-    uintptr_t base = (reinterpret_cast<uintptr_t>(a.workspace) + 255) & ~uintptr_t(255);
+    uintptr_t base = (reinterpret_cast<uintptr_t>(scratch) + 255) & ~uintptr_t(255);
     p.part_o = reinterpret_cast<float*>(base);
     p.part_ml = p.part_o + slots * a.head_dim;
   }
   p.status = device_status_ptr();
-  LA_REQUIRE(p.status != nullptr, LA_ERR_CUDA, "la_prefill_fwd: device status word unavailable");
+  LA_REQUIRE(p.status != nullptr, LA_ERR_CUDA, "%s: device status word unavailable", who);
   const bool bf16 = a.q_dtype == LA_DTYPE_BF16;
   if (a.head_dim == 128) return bf16 ? launch_tc<128, true>(a, p, mp, pl, stream) : launch_tc<128, false>(a, p, mp, pl, stream);
   return bf16 ? launch_tc<64, true>(a, p, mp, pl, stream) : launch_tc<64, false>(a, p, mp, pl, stream);
+}
+
+}  // namespace
+
+int launch_tc_prefill(const LaPrefillArgs& a, cudaStream_t stream) {
+  return launch_tc_with_scratch(a, stream, a.workspace, a.workspace_bytes, true, "la_prefill_fwd");
 }
 
 }  // namespace la
@@ -1202,31 +1395,6 @@ int noalloc_scratch(void** out) {
   return LA_OK;
 }
 
-// Tensor maps encoded into caller-provided storage, without the host-side cache.
-int encode_maps_uncached(const LaPrefillArgs& a, MapPair* mp) {
-  EncodeTiledFn enc = get_encode_tiled();
-  LA_REQUIRE(enc != nullptr, LA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  const int D = a.head_dim;
-  const cuuint64_t n_idx = (cuuint64_t)a.num_blocks * (cuuint64_t)(a.kc_stride_block / a.kc_stride_head);
-  const CUtensorMapDataType dt =
-      a.q_dtype == LA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  cuuint32_t es[5] = {1, 1, 1, 1, 1};
-  cuuint64_t dim_k[5] = {8, 8, (cuuint64_t)D / 8, 2, n_idx};
-  cuuint64_t str_k[4] = {16, 256, 128, (cuuint64_t)a.kc_stride_head * 2};
-  cuuint32_t box_k[5] = {8, 8, (cuuint32_t)D / 8, 2, 1};
-  CUresult r = enc(&mp->k, dt, 5, const_cast<void*>(a.k_cache), dim_k, str_k, box_k, es,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  LA_REQUIRE(r == CUDA_SUCCESS, LA_ERR_CUDA, "cuTensorMapEncodeTiled(K cache) failed with %d", (int)r);
-  cuuint64_t dim_v[5] = {8, 8, 2, (cuuint64_t)D / 8, n_idx};
-  cuuint64_t str_v[4] = {32, 16, 256, (cuuint64_t)a.vc_stride_head * 2};
-  cuuint32_t box_v[5] = {8, 8, 2, (cuuint32_t)D / 8, 1};
-  r = enc(&mp->v, dt, 5, const_cast<void*>(a.v_cache), dim_v, str_v, box_v, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  LA_REQUIRE(r == CUDA_SUCCESS, LA_ERR_CUDA, "cuTensorMapEncodeTiled(V cache) failed with %d", (int)r);
-  return LA_OK;
-}
-
 }  // namespace
 }  // namespace la
 
@@ -1246,41 +1414,17 @@ extern "C" int la_prefill_fwd_noalloc(const LaPrefillArgs* args, void* stream) {
   void* scratch = nullptr;
   rc = noalloc_scratch(&scratch);
   if (rc != LA_OK) return rc;
-  const LaPrefillArgs& a = *args;
-  MapPair mp;
-  TcParams p{};
-  rc = a.kv_dtype == a.q_dtype ? encode_maps_uncached(a, &mp) : cache_access(a, p, &mp);
-  if (rc != LA_OK) return rc;
-  const TcPlan pl = make_plan(a);
-  p.q = a.q; p.k = a.k; p.v = a.v; p.out = a.out;
-  p.q_st = a.q_stride_t; p.q_sh = a.q_stride_h;
-  p.k_st = a.k_stride_t; p.k_sh = a.k_stride_h;
-  p.v_st = a.v_stride_t; p.v_sh = a.v_stride_h;
-  p.o_st = a.o_stride_t; p.o_sh = a.o_stride_h;
-  p.block_table = a.block_table; p.q_offset = a.q_offset; p.q_mask = a.q_mask;
-  p.table_stride = a.table_stride;
-  p.qsl = a.query_start_loc; p.seq_lens = a.seq_lens; p.is_lazy = a.is_lazy;
-  p.cs = a.cos_sin_cache; p.cs_rows = a.cos_sin_rows;
-  p.Hq = a.num_q_heads; p.Hkv = a.num_kv_heads; p.G = a.num_q_heads / a.num_kv_heads;
-  p.g_shift = ilog2(p.G);
-  p.rot_mode = a.rot_mode; p.is_mepic = a.is_mepic; p.skip_decode = a.skip_decode;
-  p.n_splits = pl.n_splits;
-  p.page_ratio = (int)(a.kc_stride_block / a.kc_stride_head);
-  p.scale_log2 = a.sm_scale * 1.4426950408889634f;
-  p.peer = a.peer;
-  p.rows_cap = pl.rows_cap;
-  if (pl.n_splits > 1) {
-    // Every slot the merge kernel reads is written by the attention kernel of
-    // the same call (empty splits write a neutral entry), so nothing in the
-    // scratch has to be cleared between calls.
-    const size_t slots = (size_t)a.batch * a.num_kv_heads * pl.rows_cap * pl.n_splits;
-    p.part_o = reinterpret_cast<float*>(scratch);
-    p.part_ml = p.part_o + slots * a.head_dim;
-  }
-  p.status = device_status_ptr();
-  LA_REQUIRE(p.status != nullptr, LA_ERR_CUDA, "la_prefill_fwd_noalloc: device status word unavailable");
-  const bool bf16 = a.q_dtype == LA_DTYPE_BF16;
-  cudaStream_t s = (cudaStream_t)stream;
-  if (a.head_dim == 128) return bf16 ? launch_tc<128, true>(a, p, mp, pl, s) : launch_tc<128, false>(a, p, mp, pl, s);
-  return bf16 ? launch_tc<64, true>(a, p, mp, pl, s) : launch_tc<64, false>(a, p, mp, pl, s);
+  // the tensor maps are encoded into this call's own storage (the shared table of
+  // remembered maps may grow, i.e. allocate host memory)
+  return launch_tc_with_scratch(*args, (cudaStream_t)stream, scratch, kNoAllocScratchBytes, false,
+                                "la_prefill_fwd_noalloc");
 }
+
+#ifdef LA_TRACE
+// Copies the timeline of the last traced launch to the host (tuning builds only).
+extern "C" int la_trace_read(long long* out) {
+  LA_CHECK_CUDA(cudaDeviceSynchronize());
+  LA_CHECK_CUDA(cudaMemcpyFromSymbol(out, la::g_trace, sizeof(long long) * la::kTraceRows * la::kTraceCols));
+  return LA_OK;
+}
+#endif

@@ -232,6 +232,21 @@ def test_decode_per_token_rotation_split_kv(geom, kv):
     util.assert_close(got, want, what=f"per-token split-KV decode {kv}", **(FP8 if "fp8" in kv else HALF))
 
 
+@pytest.mark.parametrize("variant,op", [("lazy", "lazy_op"), ("mepic", "mepic_op")])
+@pytest.mark.parametrize("bound", [None, 0, 100, 2000])
+def test_decode_covers_sequences_longer_than_max_seq_len(variant, op, bound):
+    """``max_seq_len`` only plans the split of the KV range (the reference's decode
+    kernel ignores it and walks to ``seq_len``): a bound that is missing, zero or
+    smaller than the real lengths must not drop any cached page."""
+    docs = [[512] * 9, [500, 17, 1023], [16], [700, 700, 3] * 3, [33] * 9]
+    case = synth.build_decode(synth.GEOM_8B, torch.bfloat16, docs, seed=23, device="cuda", kv_dtype="fp8_e4m3",
+                              k_scale=0.09, v_scale=0.13, variant=variant)
+    want = util.run_oracle(case, op)
+    case["max_seq_len"] = bound
+    got = util.run_cuda(case, op, kernel="tensor")
+    util.assert_close(got, want, what=f"decode with max_seq_len={bound}", **FP8)
+
+
 def test_empty_batch_and_skip_decode_leave_output_untouched():
     import lazy_attention_b200 as la
     case = util.to_device(util.load_golden("lazy_prefill_small"), "cuda")

@@ -291,20 +291,27 @@ __device__ __forceinline__ void rotate_chunk_f16(uint4& a, uint4& b, const uint4
   }
 }
 
-template <int D>
+// PAIR: two CTAs of a cluster run every MMA together (M = 256, 128 rows of each row tile
+// per CTA).  Each CTA then holds only half of every K tile (64 of its 128 keys) and half of
+// every V tile (64 of the D dims of all 128 keys), so a stage is half as large and the ring
+// twice as deep.
+template <int D, bool PAIR = false>
 struct TcCfg {
-  static constexpr int kStages = (D == 128) ? 2 : 4;
+  static constexpr int kStages = ((D == 128) ? 2 : 4) * (PAIR ? 2 : 1);
   static constexpr int kPageBytes = D * 16 * 2;            // one page of one head, 16-bit elements
   static constexpr int kTileBytes = kPageBytes * kPagesPerTile;
+  static constexpr int kKStageBytes = PAIR ? kTileBytes / 2 : kTileBytes;   // this CTA's part of a K tile
+  static constexpr int kVPageBytes = PAIR ? kPageBytes / 2 : kPageBytes;    // this CTA's part of a V page
+  static constexpr int kVStageBytes = kVPageBytes * kPagesPerTile;
   static constexpr int kQBytes = 2 * 128 * D * 2;
   static constexpr int kRowGroupBytes = D * 16;            // 8 rows x D x 2 B
-  static constexpr int kSmemBytes = kQBytes + 2 * kStages * kTileBytes + 1024;
+  static constexpr int kSmemBytes = kQBytes + kStages * (kKStageBytes + kVStageBytes) + 1024;
 };
 
-template <int D, bool BF16, int KVF8>
-__global__ void __launch_bounds__(kThreadsTc, 1)
-prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, TcParams p) {
-  using Cfg = TcCfg<D>;
+template <int D, bool BF16, int KVF8, bool PAIR>
+__device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const CUtensorMap& mapV, const TcParams& p) {
+  static_assert(!PAIR || KVF8 == 0, "CTA pairs are implemented for 16-bit caches");
+  using Cfg = TcCfg<D, PAIR>;
   constexpr int KS = Cfg::kStages;
   constexpr int NCH = D / 8;  // 16-byte chunks per row
   constexpr bool MB = BF16 && KVF8 == 0;  // MMA operand type: bf16, else f16 (always f16 with an fp8 cache)
@@ -313,7 +320,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + Cfg::kQBytes;
-  uint8_t* sV = sK + KS * Cfg::kTileBytes;
+  uint8_t* sV = sK + KS * Cfg::kKStageBytes;
   __shared__ __align__(8) uint64_t bar_k_tma[KS], bar_k_ready[KS], bar_k_empty[KS];
   __shared__ __align__(8) uint64_t bar_v_tma[KS], bar_v_ready[KS], bar_v_empty[KS];
   __shared__ __align__(8) uint64_t bar_s_full[2], bar_p_full[2], bar_o_done, bar_q_ready;
@@ -331,11 +338,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
   const int G = p.G;
   const int nrows = qlen * G;
   const int row0 = mb * kRowsPerCta;
-  if (row0 >= nrows) return;
+  // In a pair both CTAs take every decision about the tile range from the pair's rows, so
+  // that they agree on it: a CTA whose own rows lie past the request's last row still loads
+  // and stages its halves of the K/V tiles for its partner.
+  const uint32_t cta_rank = PAIR ? cluster_cta_rank() : 0u;
+  const int row0_pair = PAIR ? (mb & ~1) * kRowsPerCta : row0;
+  constexpr int kRowsPerUnit = PAIR ? 2 * kRowsPerCta : kRowsPerCta;
+  if (row0_pair >= nrows) return;
   const int ctx = p.seq_lens[b] - qlen;
   const int ctx_pages = (ctx + 15) >> 4;
   const int n_ctx = (ctx_pages + kPagesPerTile - 1) / kPagesPerTile;
-  const int tok_hi = min(qlen - 1, (row0 + kRowsPerCta - 1) >> p.g_shift);
+  const int tok_hi = min(qlen - 1, (row0_pair + kRowsPerUnit - 1) >> p.g_shift);
   const int n_self = tok_hi / kTileN + 1;
   const int total = n_ctx + n_self;
   const int j0 = (int)((int64_t)total * split / p.n_splits);
@@ -345,30 +358,50 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
   const int32_t* off_row = p.q_offset ? p.q_offset + (int64_t)b * p.table_stride : nullptr;
   const int32_t* msk_row = p.q_mask ? p.q_mask + (int64_t)b * p.table_stride : nullptr;
 
+  // Barriers the MMA-issuing thread waits on collect the arrivals of both CTAs of a pair
+  // (they live in the pair's first CTA, the only one that issues MMAs); the barriers the MMA
+  // completions signal exist in both CTAs and are signalled in both.
+  constexpr uint32_t kProducers = PAIR ? 2 : 1;
   if (tid == 0) {
     for (int i = 0; i < KS; ++i) {
       mbar_init(&bar_k_tma[i], 1);
-      mbar_init(&bar_k_ready[i], 128);
+      mbar_init(&bar_k_ready[i], 128 * kProducers);
       mbar_init(&bar_k_empty[i], 1);
       mbar_init(&bar_v_tma[i], 1);
-      mbar_init(&bar_v_ready[i], 128);
+      mbar_init(&bar_v_ready[i], 128 * kProducers);
       mbar_init(&bar_v_empty[i], 1);
     }
     mbar_init(&bar_s_full[0], 1);
     mbar_init(&bar_s_full[1], 1);
-    mbar_init(&bar_p_full[0], 128);
-    mbar_init(&bar_p_full[1], 128);
+    mbar_init(&bar_p_full[0], 128 * kProducers);
+    mbar_init(&bar_p_full[1], 128 * kProducers);
     mbar_init(&bar_o_done, 1);
-    mbar_init(&bar_q_ready, kSoftmaxThreads);
+    mbar_init(&bar_q_ready, kSoftmaxThreads * kProducers);
     mbar_fence_init();
   }
   if (warp == kWarpMma) {
-    tmem_alloc(&tmem_base_s, 512);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(&tmem_base_s, 512);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&tmem_base_s, 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  // no thread may touch the partner's barriers before the partner has initialised them
+  if constexpr (PAIR) cluster_sync_all();
   tc_fence_after_sync();
+  // Arrival on a barrier of the MMA-issuing CTA: local in the single-CTA kernel and in the
+  // pair's first CTA, through the cluster window from the second.
+  auto arrive_at_leader = [&](uint64_t* bar) {
+    if constexpr (PAIR) {
+      mbar_arrive_cluster(map_to_cta(smem_u32(bar), 0));
+    } else {
+      mbar_arrive(bar);
+    }
+  };
   const uint32_t tmem = tmem_base_s;
   const int ntiles = j1 - j0;
   // fp8 caches: the K scale folds into the score scale of the cached tiles, the V
@@ -409,7 +442,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
         *reinterpret_cast<uint4*>(sQ + (row >> 3) * Cfg::kRowGroupBytes + g * 128 + (row & 7) * 16) = val;
       }
       fence_proxy_async_smem();
-      mbar_arrive(&bar_q_ready);
+      arrive_at_leader(&bar_q_ready);
     }
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
@@ -621,7 +654,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
         l_sum = fmaf((acc_a.x + acc_a.y) + (acc_b.x + acc_b.y), kUnbias, l_sum);
         tmem_st_wait();
         tc_fence_before_sync();
-        mbar_arrive(&bar_p_full[t]);
+        arrive_at_leader(&bar_p_full[t]);
         LA_STAMP(t * 8 + 6, j - j0);
         continue;
       }
@@ -645,7 +678,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
       LA_STAMP(t * 8 + 5, j - j0);
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(&bar_p_full[t]);
+      arrive_at_leader(&bar_p_full[t]);
       LA_STAMP(t * 8 + 6, j - j0);
     }
     // ---- epilogue: each thread writes its row
@@ -775,8 +808,107 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
     int rot_next = KVF8 != 0 ? page_rot(j0) : 0;
     for (int j = j0; j < j1 && ok; ++j) {
       const int st = (j - j0) % KS, u = (j - j0) / KS;
-      uint8_t* kst = sK + st * Cfg::kTileBytes;
-      uint8_t* vst = sV + st * Cfg::kTileBytes;
+      uint8_t* kst = sK + st * Cfg::kKStageBytes;
+      uint8_t* vst = sV + st * Cfg::kVStageBytes;
+      if constexpr (PAIR) {
+        // ---- CTA pair: this CTA stages its 64 keys of the K tile (two threads per key, each
+        // rotating half of the row) and, for new-token tiles, its half of the head dimension
+        // of V for all 128 keys.
+        const int key = i & 63, hc = i >> 6;
+        constexpr int NP = NCH / 4;  // (chunk, chunk + NCH/2) pairs per thread
+        const int g0 = hc * NP;
+        uint8_t* rowp = kst + (key >> 3) * Cfg::kRowGroupBytes + (key & 7) * 16;
+        if (j < n_ctx) {
+          const int page = j * kPagesPerTile + 4 * (int)cta_rank + (key >> 4);
+          int pos = 0;
+          if (lazy && page < ctx_pages) {
+            const int rot = off_row ? off_row[page] : 0;
+            if (p.rot_mode == LA_ROT_LAZY) {
+              pos = rot != 0 ? rot - 1 : 0;
+            } else {
+              pos = p.is_mepic ? (page * 16 + (key & 15)) : ((rot != 0 ? rot - 1 : page * 16) + (key & 15));
+            }
+            if (pos >= p.cs_rows) pos = (int)p.cs_rows - 1;
+          }
+          const uint8_t* crow = cs + (int64_t)pos * D * 2;
+          uint4 cv[NP], sv[NP];
+          if (pos > 0) {
+#pragma unroll
+            for (int g = 0; g < NP; ++g) {
+              cv[g] = __ldg(reinterpret_cast<const uint4*>(crow + (g0 + g) * 16));
+              sv[g] = __ldg(reinterpret_cast<const uint4*>(crow + D + (g0 + g) * 16));
+            }
+          }
+          ok = mbar_wait(&bar_k_tma[st], (uint32_t)u & 1u, p.status, 201);
+          if (!ok) break;
+          if (pos > 0) {
+#pragma unroll
+            for (int g = 0; g < NP; ++g) {
+              uint4 a = *reinterpret_cast<uint4*>(rowp + (g0 + g) * 128);
+              uint4 bq = *reinterpret_cast<uint4*>(rowp + (g0 + g + NCH / 2) * 128);
+              rotate_chunk<BF16>(a, bq, cv[g], sv[g]);
+              *reinterpret_cast<uint4*>(rowp + (g0 + g) * 128) = a;
+              *reinterpret_cast<uint4*>(rowp + (g0 + g + NCH / 2) * 128) = bq;
+            }
+          }
+          fence_proxy_async_smem();
+          arrive_at_leader(&bar_k_ready[st]);
+          LA_STAMP(20, j - j0);
+        } else {
+          if (u > 0) ok = mbar_wait(&bar_k_empty[st], (uint32_t)(u - 1) & 1u, p.status, 202);
+          if (!ok) break;
+          {
+            const int n = (j - n_ctx) * kTileN + 64 * (int)cta_rank + key;
+            const bool present = n < qlen;
+            const uint8_t* krow = reinterpret_cast<const uint8_t*>(p.k) +
+                                  ((int64_t)(s0 + n) * p.k_st + (int64_t)kvh * p.k_sh) * 2;
+            int pos = 0;
+            if (present && p.rot_mode == LA_ROT_MEPIC) {
+              pos = ctx + n;
+              if (pos >= p.cs_rows) pos = (int)p.cs_rows - 1;
+            }
+            const uint8_t* crow = cs + (int64_t)pos * D * 2;
+#pragma unroll
+            for (int g = 0; g < NP; ++g) {
+              uint4 a = make_uint4(0, 0, 0, 0), bq = make_uint4(0, 0, 0, 0);
+              if (present) {
+                a = *reinterpret_cast<const uint4*>(krow + (g0 + g) * 16);
+                bq = *reinterpret_cast<const uint4*>(krow + (g0 + g + NCH / 2) * 16);
+                if (pos > 0) {
+                  const uint4 cvv = __ldg(reinterpret_cast<const uint4*>(crow + (g0 + g) * 16));
+                  const uint4 svv = __ldg(reinterpret_cast<const uint4*>(crow + D + (g0 + g) * 16));
+                  rotate_chunk<BF16>(a, bq, cvv, svv);
+                }
+              }
+              *reinterpret_cast<uint4*>(rowp + (g0 + g) * 128) = a;
+              *reinterpret_cast<uint4*>(rowp + (g0 + g + NCH / 2) * 128) = bq;
+            }
+          }
+          fence_proxy_async_smem();
+          arrive_at_leader(&bar_k_ready[st]);
+          if (u > 0) ok = mbar_wait(&bar_v_empty[st], (uint32_t)(u - 1) & 1u, p.status, 203);
+          if (!ok) break;
+          {
+            // V: thread i holds key i of the tile; this CTA keeps dims [rank * D/2, +D/2), transposed
+            const int nv = (j - n_ctx) * kTileN + i;
+            const bool presentv = nv < qlen;
+            const uint8_t* vrow = reinterpret_cast<const uint8_t*>(p.v) +
+                                  ((int64_t)(s0 + nv) * p.v_st + (int64_t)kvh * p.v_sh) * 2 + (int)cta_rank * D;
+            uint8_t* base = vst + (i >> 4) * Cfg::kVPageBytes + ((i & 15) >> 3) * 128 + (i & 7) * 2;
+#pragma unroll 2
+            for (int g = 0; g < NCH / 2; ++g) {
+              uint4 val = make_uint4(0, 0, 0, 0);
+              if (presentv) val = *reinterpret_cast<const uint4*>(vrow + g * 16);
+              const uint16_t* e = reinterpret_cast<const uint16_t*>(&val);
+#pragma unroll
+              for (int x = 0; x < 8; ++x) *reinterpret_cast<uint16_t*>(base + g * 256 + x * 16) = e[x];
+            }
+          }
+          fence_proxy_async_smem();
+          arrive_at_leader(&bar_v_ready[st]);
+        }
+        continue;
+      }
       int rot;
       if constexpr (KVF8 != 0) {
         rot = rot_next;
@@ -950,36 +1082,50 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
     }
   } else if (warp == kWarpMma) {
     // =============================== MMA issue ===============================
-    if (ntiles > 0) {
+    // In a pair only the first CTA issues: each MMA covers the 128 rows of a row tile in both
+    // CTAs (M = 256), reading Q and P from each CTA and half of K / V from each CTA.
+    if (ntiles > 0 && cta_rank == 0) {
       const bool issuer = lane == 0;
-      constexpr uint32_t idesc_qk = idesc_f16(MB ? 1 : 0, 128, kTileN);
-      constexpr uint32_t idesc_pv = idesc_f16(MB ? 1 : 0, 128, D);
-      bool ok = mbar_wait(&bar_q_ready, 0, p.status, 301);
+      constexpr int kM = PAIR ? 256 : 128;
+      constexpr uint32_t idesc_qk = idesc_f16(MB ? 1 : 0, kM, kTileN);
+      constexpr uint32_t idesc_pv = idesc_f16(MB ? 1 : 0, kM, D);
+      auto wait_in = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+        return mbar_wait(bar, parity, p.status, code);
+      };
+      auto commit = [&](uint64_t* bar) {
+        if constexpr (PAIR) mma_commit_pair(bar); else mma_commit(bar);
+      };
+      bool ok = wait_in(&bar_q_ready, 0, 301);
       uint32_t v_ready_bits = 0;
       auto issue_qk = [&](int t, int st) {
         if (!issuer) return;
         const uint32_t qa = smem_u32(sQ) + t * (128 * D * 2);
-        const uint32_t ka = smem_u32(sK) + st * Cfg::kTileBytes;
+        const uint32_t ka = smem_u32(sK) + st * Cfg::kKStageBytes;
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks)
-          mma_ss(tmem + t * 128, smem_desc_nosw(qa + ks * 256, 128, Cfg::kRowGroupBytes),
-                 smem_desc_nosw(ka + ks * 256, 128, Cfg::kRowGroupBytes), idesc_qk, ks > 0);
-        mma_commit(&bar_s_full[t]);
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint64_t da = smem_desc_nosw(qa + ks * 256, 128, Cfg::kRowGroupBytes);
+          const uint64_t db = smem_desc_nosw(ka + ks * 256, 128, Cfg::kRowGroupBytes);
+          if constexpr (PAIR) mma_ss_pair(tmem + t * 128, da, db, idesc_qk, ks > 0);
+          else mma_ss(tmem + t * 128, da, db, idesc_qk, ks > 0);
+        }
+        commit(&bar_s_full[t]);
       };
       auto issue_pv = [&](int t, int st, int npages, bool first) {
         if (!issuer) return;
-        const uint32_t va = smem_u32(sV) + st * Cfg::kTileBytes;
-        for (int pg = 0; pg < npages; ++pg)
-          mma_ts(tmem + 256 + t * 128, tmem + t * 128 + pg * 8,
-                 smem_desc_nosw(va + pg * Cfg::kPageBytes, 128, 256), idesc_pv, !(first && pg == 0));
+        const uint32_t va = smem_u32(sV) + st * Cfg::kVStageBytes;
+        for (int pg = 0; pg < npages; ++pg) {
+          const uint64_t db = smem_desc_nosw(va + pg * Cfg::kVPageBytes, 128, 256);
+          if constexpr (PAIR) mma_ts_pair(tmem + 256 + t * 128, tmem + t * 128 + pg * 8, db, idesc_pv, !(first && pg == 0));
+          else mma_ts(tmem + 256 + t * 128, tmem + t * 128 + pg * 8, db, idesc_pv, !(first && pg == 0));
+        }
       };
       if (ok) {
-        ok = mbar_wait(&bar_k_ready[0], 0, p.status, 302);
+        ok = wait_in(&bar_k_ready[0], 0, 302);
         tc_fence_after_sync();
         if (ok) {
           issue_qk(0, 0);
           issue_qk(1, 0);
-          if (issuer) mma_commit(&bar_k_empty[0]);
+          if (issuer) commit(&bar_k_empty[0]);
           __syncwarp();
         }
       }
@@ -991,38 +1137,38 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
         const int st_n = (j + 1 - j0) % KS, u_n = (j + 1 - j0) / KS;
         // V of this tile (staged by the staging warps for new tokens and for fp8 caches)
         if (self || KVF8 != 0) {
-          ok = mbar_wait(&bar_v_ready[st], (v_ready_bits >> st) & 1u, p.status, 303);
+          ok = wait_in(&bar_v_ready[st], (v_ready_bits >> st) & 1u, 303);
           v_ready_bits ^= 1u << st;
         } else {
           ok = mbar_wait(&bar_v_tma[st], (uint32_t)u & 1u, p.status, 304);
         }
         if (!ok) break;
-        ok = mbar_wait(&bar_p_full[0], (uint32_t)(j - j0) & 1u, p.status, 305);
+        ok = wait_in(&bar_p_full[0], (uint32_t)(j - j0) & 1u, 305);
         if (!ok) break;
         tc_fence_after_sync();
         LA_STAMP(16, j - j0);
         issue_pv(0, st, npages, j == j0);
         if (has_next) {
-          ok = mbar_wait(&bar_k_ready[st_n], (uint32_t)u_n & 1u, p.status, 306);
+          ok = wait_in(&bar_k_ready[st_n], (uint32_t)u_n & 1u, 306);
           if (!ok) break;
           tc_fence_after_sync();
           issue_qk(0, st_n);
         }
         LA_STAMP(17, j - j0);
-        ok = mbar_wait(&bar_p_full[1], (uint32_t)(j - j0) & 1u, p.status, 307);
+        ok = wait_in(&bar_p_full[1], (uint32_t)(j - j0) & 1u, 307);
         if (!ok) break;
         tc_fence_after_sync();
         LA_STAMP(18, j - j0);
         issue_pv(1, st, npages, j == j0);
-        if (issuer) mma_commit(&bar_v_empty[st]);
+        if (issuer) commit(&bar_v_empty[st]);
         if (has_next) {
           issue_qk(1, st_n);
-          if (issuer) mma_commit(&bar_k_empty[st_n]);
+          if (issuer) commit(&bar_k_empty[st_n]);
         }
         LA_STAMP(19, j - j0);
         __syncwarp();
       }
-      if (ok && issuer) mma_commit(&bar_o_done);
+      if (ok && issuer) commit(&bar_o_done);
       __syncwarp();
       }
   } else {
@@ -1036,6 +1182,26 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
       if (lane < npages) coord = bt_row[j * kPagesPerTile + lane] * p.page_ratio + kvh;
       if (u > 0) ok = mbar_wait(&bar_k_empty[st], (uint32_t)(u - 1) & 1u, p.status, 401);
       if (!ok) break;
+      if constexpr (PAIR) {
+        // K: this CTA's four pages of the tile, counted on its own barrier (its staging warps
+        // rotate them before the pair's MMA thread hears of them).
+        const int mine = max(0, min(4, npages - 4 * (int)cta_rank));
+        const int kcoord = __shfl_sync(0xffffffffu, coord, (lane + 4 * (int)cta_rank) & 31);
+        if (lane == 0) mbar_arrive_expect_tx(&bar_k_tma[st], (uint32_t)mine * Cfg::kPageBytes);
+        __syncwarp();
+        if (lane < mine)
+          tma_load_5d(sK + st * Cfg::kKStageBytes + lane * Cfg::kPageBytes, &mapK, &bar_k_tma[st], 0, 0, 0, 0, kcoord);
+        if (u > 0) ok = mbar_wait(&bar_v_empty[st], (uint32_t)(u - 1) & 1u, p.status, 402);
+        if (!ok) break;
+        // V: this CTA's half of the head dimension of every page; both CTAs' copies are
+        // counted on the first CTA's barrier, which expects the bytes of both halves.
+        if (lane == 0 && cta_rank == 0) mbar_arrive_expect_tx(&bar_v_tma[st], (uint32_t)npages * Cfg::kPageBytes);
+        __syncwarp();
+        if (lane < npages)
+          tma_load_5d_pair(sV + st * Cfg::kVStageBytes + lane * Cfg::kVPageBytes, &mapV,
+                           map_to_cta(smem_u32(&bar_v_tma[st]), 0), 0, 0, 0, (int)cta_rank * (D / 16), coord);
+        continue;
+      }
       if (lane == 0) mbar_arrive_expect_tx(&bar_k_tma[st], (uint32_t)npages * Cfg::kPageBytes);
       __syncwarp();
       if (lane < npages)
@@ -1052,7 +1218,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
   // ---- teardown: every role is done (or has given up); release tensor memory
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == kWarpMma) tmem_dealloc(tmem, 512);
+  if constexpr (PAIR) {
+    // neither CTA may leave (its shared memory holds barriers the partner signals and
+    // operands the pair's MMAs read) before both are done
+    cluster_sync_all();
+    if (warp == kWarpMma) tmem_dealloc_pair(tmem, 512);
+  } else {
+    if (warp == kWarpMma) tmem_dealloc(tmem, 512);
+  }
+}
+
+template <int D, bool BF16, int KVF8>
+__global__ void __launch_bounds__(kThreadsTc, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, TcParams p) {
+  prefill_tc_body<D, BF16, KVF8, false>(mapK, mapV, p);
+}
+
+// The same kernel run by clusters of two CTAs (consecutive row blocks of one request and KV
+// head), 16-bit caches only.  mapV copies half of the head dimension of a page.
+template <int D, bool BF16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsTc, 1)
+prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, TcParams p) {
+  prefill_tc_body<D, BF16, 0, true>(mapK, mapV, p);
 }
 
 // Merge the per-split partial results: out = sum_s 2^(m_s - m*) O_s / sum_s 2^(m_s - m*) l_s.
@@ -1100,16 +1287,16 @@ struct MapKey {
   const void* kc;
   const void* vc;
   int64_t nb, ksb, ksh, vsb, vsh;
-  int D, dt;
+  int D, dt, half_v;
   bool operator==(const MapKey& o) const {
     return kc == o.kc && vc == o.vc && nb == o.nb && ksb == o.ksb && ksh == o.ksh && vsb == o.vsb &&
-           vsh == o.vsh && D == o.D && dt == o.dt;
+           vsh == o.vsh && D == o.D && dt == o.dt && half_v == o.half_v;
   }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
     size_t h = std::hash<const void*>()(k.kc) ^ (std::hash<const void*>()(k.vc) << 1);
-    h ^= std::hash<int64_t>()(k.nb * 131 + k.ksb * 17 + k.ksh + k.D * 7 + k.dt);
+    h ^= std::hash<int64_t>()(k.nb * 131 + k.ksb * 17 + k.ksh + k.D * 7 + k.dt + k.half_v * 3);
     return h;
   }
 };
@@ -1120,8 +1307,9 @@ std::mutex g_map_mu;
 std::unordered_map<MapKey, MapPair, MapKeyHash> g_maps;
 
 // The two tensor maps of a 16-bit cache: one page of one head per box, laid out
-// for the no-swizzle operand layout (see the head of this file).
-int encode_maps(const LaPrefillArgs& a, MapPair* mp) {
+// for the no-swizzle operand layout (see the head of this file).  half_v: the V box covers
+// half of the head dimension (the kernel run by CTA pairs, where each CTA keeps one half).
+int encode_maps(const LaPrefillArgs& a, bool half_v, MapPair* mp) {
   EncodeTiledFn enc = get_encode_tiled();
   LA_REQUIRE(enc != nullptr, LA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const int D = a.head_dim;
@@ -1145,7 +1333,7 @@ int encode_maps(const LaPrefillArgs& a, MapPair* mp) {
     // 8 tokens, 8 dims, 2 token halves, D/8 dim groups, (page, head)
     cuuint64_t dim[5] = {8, 8, 2, (cuuint64_t)D / 8, n_idx};
     cuuint64_t str[4] = {32, 16, 256, (cuuint64_t)a.vc_stride_head * 2};
-    cuuint32_t box[5] = {8, 8, 2, (cuuint32_t)D / 8, 1};
+    cuuint32_t box[5] = {8, 8, 2, (cuuint32_t)D / (half_v ? 16 : 8), 1};
     CUresult r = enc(&mp->v, dt, 5, const_cast<void*>(a.v_cache), dim, str, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -1157,9 +1345,9 @@ int encode_maps(const LaPrefillArgs& a, MapPair* mp) {
 // Tensor maps of a cache, remembered per (pointers, shape).  A layer is called again and
 // again with the same caches: the calling thread's last pair is checked first, without
 // taking the lock of the shared table.
-int cached_maps(const LaPrefillArgs& a, MapPair* out) {
+int cached_maps(const LaPrefillArgs& a, bool half_v, MapPair* out) {
   MapKey key{a.k_cache, a.v_cache, a.num_blocks, a.kc_stride_block, a.kc_stride_head,
-             a.vc_stride_block, a.vc_stride_head, a.head_dim, a.q_dtype};
+             a.vc_stride_block, a.vc_stride_head, a.head_dim, a.q_dtype, half_v ? 1 : 0};
   thread_local MapKey last_key{};
   thread_local MapPair last_pair;
   thread_local bool have_last = false;
@@ -1172,7 +1360,7 @@ int cached_maps(const LaPrefillArgs& a, MapPair* out) {
     auto it = g_maps.find(key);
     if (it == g_maps.end()) {
       MapPair mp;
-      int rc = encode_maps(a, &mp);
+      int rc = encode_maps(a, half_v, &mp);
       if (rc != LA_OK) return rc;
       if (g_maps.size() > 4096) g_maps.clear();
       it = g_maps.emplace(key, mp).first;
@@ -1193,6 +1381,7 @@ int ilog2(int v) {
 
 struct TcPlan {
   int mblocks, n_splits;
+  bool pair;             // run by clusters of two CTAs (consecutive row blocks)
   int64_t rows_cap;
   size_t scratch_bytes;  // split-KV partials (0 when the KV range is not split)
 };
@@ -1201,6 +1390,14 @@ TcPlan make_plan(const LaPrefillArgs& a) {
   const int G = a.num_q_heads / a.num_kv_heads;
   TcPlan pl;
   pl.mblocks = (int)(((int64_t)a.max_query_len * G + kRowsPerCta - 1) / kRowsPerCta);
+  // CTA pairs: 16-bit caches, and at least two row blocks per (request, KV head) so that a
+  // pair is not half empty by construction.
+  pl.pair = a.kv_dtype == a.q_dtype && pl.mblocks >= 2;
+  if (const char* e = getenv("LAZY_ATTN_B200_PREFILL_PAIR")) {  // experiments only
+    if (e[0] == '0') pl.pair = false;
+    if (e[0] == '1' && a.kv_dtype == a.q_dtype) pl.pair = true;
+  }
+  if (pl.pair) pl.mblocks = (pl.mblocks + 1) & ~1;
   pl.rows_cap = (int64_t)pl.mblocks * kRowsPerCta;
   // Split the KV range when the row blocks alone cannot fill the GPU.  The
   // sequence lengths live on the device, so the plan uses the caller's maxima.
@@ -1291,7 +1488,34 @@ int launch_tc_kv(const LaPrefillArgs& a, const TcParams& p, const MapPair& mp, c
 }
 
 template <int D, bool BF16>
+int launch_tc_pair(const LaPrefillArgs& a, const TcParams& p, const MapPair& mp, const TcPlan& pl,
+                   cudaStream_t stream) {
+  using Cfg = TcCfg<D, true>;
+  auto kern = prefill_tc_pair_kernel<D, BF16>;
+  static std::atomic<uint64_t> prepared{0};
+  int dev = 0;
+  LA_CHECK_CUDA(cudaGetDevice(&dev));
+  if (((prepared.load(std::memory_order_acquire) >> (dev & 63)) & 1ull) == 0) {
+    LA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    prepared.fetch_or(1ull << (dev & 63), std::memory_order_release);
+  }
+  dim3 grid(pl.mblocks, a.num_kv_heads, a.batch * pl.n_splits);  // x is even: clusters of (2, 1, 1)
+  kern<<<grid, kThreadsTc, Cfg::kSmemBytes, stream>>>(mp.k, mp.v, p);
+  count_launch();
+  LA_CHECK_CUDA(cudaGetLastError());
+  if (pl.n_splits > 1) {
+    constexpr int kRowsPerBlock = 256 / (D / 4);
+    dim3 cgrid((unsigned)((pl.rows_cap + kRowsPerBlock - 1) / kRowsPerBlock), a.num_kv_heads, a.batch);
+    prefill_combine_kernel<D, BF16><<<cgrid, 256, 0, stream>>>(p);
+    count_launch();
+    LA_CHECK_CUDA(cudaGetLastError());
+  }
+  return LA_OK;
+}
+
+template <int D, bool BF16>
 int launch_tc(const LaPrefillArgs& a, const TcParams& p, const MapPair& mp, const TcPlan& pl, cudaStream_t stream) {
+  if (pl.pair) return launch_tc_pair<D, BF16>(a, p, mp, pl, stream);
   if (a.kv_dtype == LA_DTYPE_FP8_E4M3) return launch_tc_kv<D, BF16, 1>(a, p, mp, pl, stream);
   if (a.kv_dtype == LA_DTYPE_FP8_E5M2) return launch_tc_kv<D, BF16, 2>(a, p, mp, pl, stream);
   return launch_tc_kv<D, BF16, 0>(a, p, mp, pl, stream);
@@ -1313,7 +1537,7 @@ int launch_tc_with_scratch(const LaPrefillArgs& a, cudaStream_t stream, void* sc
   std::memset(&mp, 0, sizeof(mp));
   if (a.kv_dtype == a.q_dtype) {
     // 16-bit caches are read through tensor maps
-    int rc = keep_maps ? cached_maps(a, &mp) : encode_maps(a, &mp);
+    int rc = keep_maps ? cached_maps(a, pl.pair, &mp) : encode_maps(a, pl.pair, &mp);
     if (rc != LA_OK) return rc;
   } else {
     // fp8 caches are read with plain loads by the staging warps

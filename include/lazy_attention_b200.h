@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define LA_VERSION 100
+#define LA_VERSION 101
 
 /* error codes */
 #define LA_OK 0
@@ -134,6 +134,22 @@ typedef struct LaPrefillArgs {
   void* workspace;        /* split-KV scratch, see la_prefill_workspace_bytes */
   size_t workspace_bytes;
   LaPeerOut peer;         /* optional fused output gather */
+  /* Optional packed table, int64 [batch, >= pages]: block << 32 | q_offset << 16 | q_mask
+   * (what la_pack_block_table writes and the decode kernel reads,
+   * lazy_attn/lazy/worker/gpu_model_runner.py:322-330).  When non-NULL the kernels take a
+   * page's block id, rotation offset and pad count from this one 8-byte entry instead of
+   * three gathers from block_table / q_offset / q_mask (which may then be NULL); the
+   * reference's prefill kernel always does the three gathers
+   * (lazy_attn/lazy/attention/ops/prefix_prefill.py:171,180-185,267-268). */
+  const int64_t* packed_block_table;
+  int64_t packed_stride;
+  /* Optional fused cache write, int64 [num_tokens]: when non-NULL the call also stores the
+   * new K/V rows of its requests into the paged caches at these slots (negative = skip),
+   * exactly as la_write_paged_cache does -- the step that precedes the attention op in
+   * lazy_attn/lazy/attention/backends/triton_attn.py:100-109 -- so that the separate launch
+   * can be dropped.  The caches are written through k_cache / v_cache although the struct
+   * declares them const.  Requests the call skips (skip_decode) are not written. */
+  const int64_t* slot_mapping;
 } LaPrefillArgs;
 
 /*
@@ -188,6 +204,14 @@ typedef struct LaDecodeArgs {
   void* workspace; /* split-KV scratch, see la_decode_workspace_bytes */
   size_t workspace_bytes;
   LaPeerOut peer;  /* optional fused output gather */
+  /* Optional fused cache write for the decode rows: key / value [num_tokens, Hkv, D] of the
+   * step and slot_mapping int64 [num_tokens].  When slot_mapping is non-NULL the kernel
+   * stores each sequence's new K/V row into the caches (as la_write_paged_cache would have
+   * before the call) and attends to it; seq_lens counts the new token, as in the reference. */
+  const void* key;
+  const void* value;
+  int64_t k_stride_t, k_stride_h, v_stride_t, v_stride_h;
+  const int64_t* slot_mapping;
 } LaDecodeArgs;
 
 /* Replaces context_attention_fwd / _fwd_kernel (see LaPrefillArgs). */

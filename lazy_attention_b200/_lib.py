@@ -64,6 +64,8 @@ class LaPrefillArgs(C.Structure):
         ("sm_scale", C.c_float), ("kernel", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("peer", LaPeerOut),
+        ("packed_block_table", C.c_void_p), ("packed_stride", C.c_int64),
+        ("slot_mapping", C.c_void_p),
     ]
 
 
@@ -89,6 +91,10 @@ class LaDecodeArgs(C.Structure):
         ("ignore_q_mask", C.c_int32), ("sm_scale", C.c_float), ("kernel", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("peer", LaPeerOut),
+        ("key", C.c_void_p), ("value", C.c_void_p),
+        ("k_stride_t", C.c_int64), ("k_stride_h", C.c_int64),
+        ("v_stride_t", C.c_int64), ("v_stride_h", C.c_int64),
+        ("slot_mapping", C.c_void_p),
     ]
 
 

@@ -141,6 +141,15 @@ def _bool_u8(t):
     raise ValueError("is_lazy must be a bool tensor")
 
 
+def _slots(slot_mapping, num_rows):
+    """Pointer of the slot mapping of a fused cache write (None: off)."""
+    if slot_mapping is None:
+        return None
+    if slot_mapping.dtype != torch.int64 or not slot_mapping.is_cuda or not slot_mapping.is_contiguous():
+        raise ValueError("slot_mapping must be a contiguous int64 CUDA tensor")
+    return slot_mapping.data_ptr()
+
+
 def _scale(t, device):
     if torch.is_tensor(t):
         if t.dtype != torch.float32 or not t.is_cuda:
@@ -149,10 +158,16 @@ def _scale(t, device):
     raise ValueError("k_scale / v_scale must be 1-element float32 device tensors")
 
 
-def _prefill(q, k, v, o, kv_cache_dtype, k_cache, v_cache, b_loc, b_start_loc, b_seq_len,
-             max_seq_len, max_input_len, k_scale, v_scale, alibi_slopes, sliding_window,
-             sm_scale, skip_decode, cos_sin_cache, rotary_dim, is_neox_style, is_lazy,
-             q_offset, q_mask, rot_mode, is_mepic, kernel, peer_out=None):
+def prefill_args(q, k, v, o, kv_cache_dtype, k_cache, v_cache, b_loc, b_start_loc, b_seq_len,
+                 max_seq_len, max_input_len, k_scale, v_scale, alibi_slopes, sliding_window,
+                 sm_scale, skip_decode, cos_sin_cache, rotary_dim, is_neox_style, is_lazy,
+                 q_offset, q_mask, rot_mode, is_mepic, kernel, peer_out=None,
+                 packed_block_table=None, slot_mapping=None) -> LaPrefillArgs:
+    """Checks the tensors of a prefix-prefill call the way the reference wrapper does
+    (ops/prefix_prefill.py:626-674: fp8 views, dtype and shape assertions, alibi refusal)
+    plus what a raw-pointer interface must know (devices, dtypes of the int tables, unit
+    inner strides, page contiguity), and fills the C struct.  Every entry point that takes
+    ``LaPrefillArgs`` goes through here.  The workspace fields are left empty."""
     kv_code = _fp8_view(kv_cache_dtype, k_cache, v_cache)
     Lq, Lk, Lv = q.shape[-1], k.shape[-1], v.shape[-1]
     assert Lq == Lk and Lk == Lv
@@ -166,7 +181,8 @@ def _prefill(q, k, v, o, kv_cache_dtype, k_cache, v_cache, b_loc, b_start_loc, b
         raise NotImplementedError("Alibi slopes are not implemented for prefix prefill")
     if not is_neox_style:
         raise NotImplementedError("only NeoX-style rotary embedding is supported")
-    _require_cuda(q, k, v, o, k_cache, v_cache, b_loc, b_start_loc, b_seq_len)
+    _require_cuda(q, k, v, o, k_cache, v_cache, b_loc, b_start_loc, b_seq_len, q_offset, q_mask,
+                  packed_block_table, is_lazy)
     if q.dtype not in _ACT or k.dtype != q.dtype or v.dtype != q.dtype or o.dtype != q.dtype:
         raise ValueError("q, k, v, o must share one dtype out of float32/float16/bfloat16")
     for t, n in ((q, "q"), (k, "k"), (v, "v"), (o, "o")):
@@ -195,11 +211,19 @@ def _prefill(q, k, v, o, kv_cache_dtype, k_cache, v_cache, b_loc, b_start_loc, b
     a.num_blocks = k_cache.shape[0]
     a.block_table, a.q_offset, a.q_mask = _ptr(b_loc), _ptr(q_offset), _ptr(q_mask)
     a.table_stride = b_loc.stride(0)
+    if packed_block_table is not None:
+        if packed_block_table.dtype != torch.int64 or packed_block_table.stride(1) != 1:
+            raise ValueError("packed_block_table must be int64 with unit inner stride")
+        if packed_block_table.shape[0] < batch:
+            raise ValueError("packed_block_table has fewer rows than the batch")
+        a.packed_block_table = packed_block_table.data_ptr()
+        a.packed_stride = packed_block_table.stride(0)
+    a.slot_mapping = _slots(slot_mapping, q.shape[0])
     a.query_start_loc, a.seq_lens = b_start_loc.data_ptr(), b_seq_len.data_ptr()
-    lazy_u8 = _bool_u8(is_lazy)
-    a.is_lazy = _ptr(lazy_u8)
-    ks, vs = _scale(k_scale, q.device), _scale(v_scale, q.device)
-    a.k_scale, a.v_scale = ks.data_ptr(), vs.data_ptr()
+    a.is_lazy = _ptr(_bool_u8(is_lazy))  # a view of the caller's tensor: same storage
+    if kv_code in (_lib.DTYPE_FP8_E4M3, _lib.DTYPE_FP8_E5M2) or k_scale is not None:
+        ks, vs = _scale(k_scale, q.device), _scale(v_scale, q.device)
+        a.k_scale, a.v_scale = ks.data_ptr(), vs.data_ptr()
     if cos_sin_cache is not None:
         _require_cuda(cos_sin_cache)
         if cos_sin_cache.dtype not in _ACT or not cos_sin_cache.is_contiguous():
@@ -223,6 +247,11 @@ def _prefill(q, k, v, o, kv_cache_dtype, k_cache, v_cache, b_loc, b_start_loc, b
     a.kernel = _kernel_choice(kernel)
     if peer_out is not None:
         peer_out.fill(a.peer)
+    return a
+
+
+def _prefill(q, k, v, o, *rest, **kw):
+    a = prefill_args(q, k, v, o, *rest, **kw)
     lib = _lib.load()
     need = lib.la_prefill_workspace_bytes(C.byref(a))
     ws = _workspace(q.device, need)
@@ -239,18 +268,25 @@ def context_attention_fwd(q, k, v, o, kv_cache_dtype: str, k_cache, v_cache, b_l
                           v_scale: torch.Tensor, alibi_slopes=None, sliding_window=None,
                           sm_scale=None, skip_decode=False, cos_sin_cache=None, rotary_dim=None,
                           is_neox_style=True, is_lazy=None, q_offset=None, q_mask=None,
-                          kernel=None, peer_out=None):
+                          kernel=None, peer_out=None, packed_block_table=None, slot_mapping=None):
     """Prefix-prefill attention, per-page rotation variant.  Writes ``o`` in place.
 
     For a lazy request every cached page's K is rotated forward by
     ``q_offset - 1`` positions (0 and 1 mean none) and the last ``q_mask``
     tokens of the page are masked; the new tokens attend causally to the new
     K/V.  Requests whose ``is_lazy`` is false take the plain paged path.
+
+    ``packed_block_table`` (not in the reference's signature; the runner keeps it
+    for the decode kernel) lets the kernel read a page's block id, offset and pad
+    count as one 8-byte entry instead of three gathers.  ``slot_mapping`` (also an
+    addition) makes the call store the new K/V rows into the caches itself: the
+    ``write_to_paged_cache`` that precedes the op in the reference backend
+    (backends/triton_attn.py:100-109) is then not needed.
     """
     _prefill(q, k, v, o, kv_cache_dtype, k_cache, v_cache, b_loc, b_start_loc, b_seq_len,
              max_seq_len, max_input_len, k_scale, v_scale, alibi_slopes, sliding_window,
              sm_scale, skip_decode, cos_sin_cache, rotary_dim, is_neox_style, is_lazy,
-             q_offset, q_mask, _lib.ROT_LAZY, False, kernel, peer_out)
+             q_offset, q_mask, _lib.ROT_LAZY, False, kernel, peer_out, packed_block_table, slot_mapping)
 
 
 @torch.inference_mode()
@@ -260,20 +296,21 @@ def context_attention_fwd_mepic(q, k, v, o, kv_cache_dtype: str, k_cache, v_cach
                                 sliding_window=None, sm_scale=None, skip_decode=False,
                                 cos_sin_cache=None, rotary_dim=None, is_neox_style=True,
                                 q_mask=None, q_offset=None, is_mepic: bool = True,
-                                force_fp32_rotary: bool = False, kernel=None, peer_out=None):
+                                force_fp32_rotary: bool = False, kernel=None, peer_out=None,
+                                packed_block_table=None, slot_mapping=None):
     """Prefix-prefill attention, per-token rotation variant: cached K is rotated
     at each token's slot position, new K at ``ctx_len + n``.  The rotation is
     always evaluated in float32 (``force_fp32_rotary`` is accepted and implied)."""
     _prefill(q, k, v, o, kv_cache_dtype, k_cache, v_cache, b_loc, b_start_loc, b_seq_len,
              max_seq_len, max_input_len, k_scale, v_scale, alibi_slopes, sliding_window,
              sm_scale, skip_decode, cos_sin_cache, rotary_dim, is_neox_style, None,
-             q_offset, q_mask, _lib.ROT_MEPIC, is_mepic, kernel, peer_out)
+             q_offset, q_mask, _lib.ROT_MEPIC, is_mepic, kernel, peer_out, packed_block_table, slot_mapping)
 
 
 def _decode(query, output, kv_cache_dtype, key_cache, value_cache, query_start_loc, seq_lens,
             max_seq_len, k_scale, v_scale, alibi_slopes, sliding_window, sm_scale, rotary_dim,
             cos_sin_cache, is_lazy, packed_block_table, block_table, q_mask, rot_mode,
-            ignore_q_mask, kernel, peer_out=None):
+            ignore_q_mask, kernel, peer_out=None, key=None, value=None, slot_mapping=None):
     kv_code = _fp8_view(kv_cache_dtype, key_cache, value_cache)
     _require_cuda(query, output, key_cache, value_cache, query_start_loc, seq_lens)
     if query.dtype not in _ACT or output.dtype != query.dtype:
@@ -332,6 +369,14 @@ def _decode(query, output, kv_cache_dtype, key_cache, value_cache, query_start_l
     a.kernel = _kernel_choice(kernel)
     if peer_out is not None:
         peer_out.fill(a.peer)
+    if slot_mapping is not None:
+        _require_cuda(key, value)
+        if key.dtype != query.dtype or value.dtype != query.dtype or key.stride(2) != 1 or value.stride(2) != 1:
+            raise ValueError("key / value must have the query's dtype and a contiguous last dimension")
+        a.key, a.value = key.data_ptr(), value.data_ptr()
+        a.k_stride_t, a.k_stride_h = key.stride(0), key.stride(1)
+        a.v_stride_t, a.v_stride_h = value.stride(0), value.stride(1)
+        a.slot_mapping = _slots(slot_mapping, query.shape[0])
     lib = _lib.load()
     need = lib.la_decode_workspace_bytes(C.byref(a))
     ws = _workspace(query.device, need)
@@ -349,7 +394,7 @@ def chunked_prefill_paged_decode(query, key, value, output, kv_cache_dtype, key_
                                  sliding_window=None, sm_scale=None, rotary_dim=None, freqs=None,
                                  cos_sin_cache=None, rope_meta=None, is_neox_style=True,
                                  is_lazy=None, lazy_variant=None, q_offset=None, q_mask=None,
-                                 packed_block_table=None, kernel=None, peer_out=None):
+                                 packed_block_table=None, kernel=None, peer_out=None, slot_mapping=None):
     """One attention-layer call on a mixed batch: prefix-prefill for requests with
     more than one query token, paged decode for those with exactly one.
 
@@ -373,7 +418,8 @@ def chunked_prefill_paged_decode(query, key, value, output, kv_cache_dtype, key_
                               sliding_window=sliding_window, sm_scale=sm_scale, skip_decode=True,
                               rotary_dim=rotary_dim, cos_sin_cache=cos_sin_cache,
                               is_neox_style=is_neox_style, is_lazy=is_lazy, q_offset=q_offset,
-                              q_mask=q_mask, kernel=kernel, peer_out=peer_out)
+                              q_mask=q_mask, kernel=kernel, peer_out=peer_out,
+                              packed_block_table=packed_block_table, slot_mapping=slot_mapping)
     table = packed_block_table
     if table is None:
         # The reference would hand the kernel the plain table and unpack garbage
@@ -382,7 +428,7 @@ def chunked_prefill_paged_decode(query, key, value, output, kv_cache_dtype, key_
     _decode(query, output, kv_cache_dtype, key_cache, value_cache, query_start_loc, seq_lens,
             max_seq_len, k_scale, v_scale, alibi_slopes, sliding_window, sm_scale, rotary_dim,
             cos_sin_cache, is_lazy, table, None, None, _lib.ROT_LAZY,
-            _env_flag("LAZY_DECODE_IGNORE_Q_MASK"), kernel, peer_out)
+            _env_flag("LAZY_DECODE_IGNORE_Q_MASK"), kernel, peer_out, key, value, slot_mapping)
 
 
 @torch.inference_mode()
@@ -392,7 +438,8 @@ def chunked_prefill_paged_decode_mepic(query, key, value, output, kv_cache_dtype
                                        alibi_slopes=None, sliding_window=None, sm_scale=None,
                                        rotary_dim=None, cos_sin_cache=None, is_neox_style=True,
                                        q_offset=None, q_mask=None, is_mepic: bool = True,
-                                       force_fp32_rotary: bool = False, kernel=None, peer_out=None):
+                                       force_fp32_rotary: bool = False, kernel=None, peer_out=None,
+                                       slot_mapping=None):
     """Per-token rotation twin of :func:`chunked_prefill_paged_decode`: plain
     int32 block table and ``q_mask``; missing ``q_mask`` / ``q_offset`` mean zeros."""
     if sm_scale is None:
@@ -415,7 +462,8 @@ def chunked_prefill_paged_decode_mepic(query, key, value, output, kv_cache_dtype
                                     cos_sin_cache=cos_sin_cache, is_neox_style=is_neox_style,
                                     q_mask=q_mask, q_offset=q_offset, is_mepic=is_mepic,
                                     force_fp32_rotary=force_fp32_rotary, kernel=kernel,
-                                    peer_out=peer_out)
+                                    peer_out=peer_out, slot_mapping=slot_mapping)
     _decode(query, output, kv_cache_dtype, key_cache, value_cache, query_start_loc, seq_lens,
             max_seq_len, k_scale, v_scale, alibi_slopes, sliding_window, sm_scale, rotary_dim,
-            cos_sin_cache, None, None, block_table, q_mask, _lib.ROT_MEPIC, False, kernel, peer_out)
+            cos_sin_cache, None, None, block_table, q_mask, _lib.ROT_MEPIC, False, kernel, peer_out,
+            key, value, slot_mapping)

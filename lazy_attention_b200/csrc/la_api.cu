@@ -41,7 +41,7 @@ int validate_prefill(const LaPrefillArgs* a) {
   LA_REQUIRE(a->batch >= 0, LA_ERR_INVALID_ARGUMENT, "la_prefill_fwd: batch %d < 0", a->batch);
   if (a->batch == 0 || a->max_query_len <= 0) return LA_OK;
   LA_REQUIRE(a->q && a->k && a->v && a->out, LA_ERR_INVALID_ARGUMENT, "la_prefill_fwd: null q/k/v/out");
-  LA_REQUIRE(a->k_cache && a->v_cache && a->block_table, LA_ERR_INVALID_ARGUMENT,
+  LA_REQUIRE(a->k_cache && a->v_cache && (a->block_table || a->packed_block_table), LA_ERR_INVALID_ARGUMENT,
              "la_prefill_fwd: null cache or block table");
   LA_REQUIRE(a->query_start_loc && a->seq_lens, LA_ERR_INVALID_ARGUMENT,
              "la_prefill_fwd: null query_start_loc / seq_lens");
@@ -63,8 +63,10 @@ int validate_prefill(const LaPrefillArgs* a) {
                "la_prefill_fwd: rotation requested without a cos/sin table");
     LA_REQUIRE(is_act_dtype(a->cos_sin_dtype), LA_ERR_INVALID_ARGUMENT,
                "la_prefill_fwd: cos/sin dtype %d", a->cos_sin_dtype);
-    LA_REQUIRE(a->q_mask != nullptr, LA_ERR_INVALID_ARGUMENT, "la_prefill_fwd: q_mask is null");
-    LA_REQUIRE(a->q_offset != nullptr || (a->rot_mode == LA_ROT_MEPIC && a->is_mepic),
+    LA_REQUIRE(a->q_mask != nullptr || a->packed_block_table != nullptr, LA_ERR_INVALID_ARGUMENT,
+               "la_prefill_fwd: q_mask is null");
+    LA_REQUIRE(a->q_offset != nullptr || a->packed_block_table != nullptr ||
+                   (a->rot_mode == LA_ROT_MEPIC && a->is_mepic),
                LA_ERR_INVALID_ARGUMENT, "la_prefill_fwd: q_offset is null");
   }
   return LA_OK;
@@ -121,9 +123,24 @@ extern "C" int la_prefill_fwd(const LaPrefillArgs* args, void* stream) {
   if (args->batch == 0 || args->max_query_len <= 0) return LA_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const char* why = "";
+  // The general kernel does not store the new K/V rows itself: where it serves the call,
+  // the fused cache write runs as a launch of its own just before it.
+  auto general = [&]() -> int {
+    const LaPrefillArgs& a = *args;
+    if (a.slot_mapping != nullptr) {
+      int wrc = write_cache_by_request(a.kv_dtype, a.q_dtype, a.query_start_loc, a.batch, a.max_query_len, 0,
+                                       a.skip_decode, a.k, a.v, const_cast<void*>(a.k_cache),
+                                       const_cast<void*>(a.v_cache), a.slot_mapping, a.k_stride_t, a.k_stride_h,
+                                       a.v_stride_t, a.v_stride_h, a.kc_stride_block, a.kc_stride_head,
+                                       a.vc_stride_block, a.vc_stride_head, a.num_kv_heads, a.head_dim, a.block_size,
+                                       a.x, a.k_scale, a.v_scale, s);
+      if (wrc != LA_OK) return wrc;
+    }
+    return launch_general_prefill(a, s);
+  };
   if (args->kernel == LA_KERNEL_GENERAL) {
     LA_REQUIRE(args->peer.num_peers == 0, LA_ERR_UNSUPPORTED, "la_prefill_fwd: the general kernel has no fused output gather");
-    return launch_general_prefill(*args, s);
+    return general();
   }
   const bool tc_ok = tc_prefill_supported(*args, &why);
   if (args->kernel == LA_KERNEL_TENSOR) {
@@ -136,7 +153,7 @@ extern "C" int la_prefill_fwd(const LaPrefillArgs* args, void* stream) {
   if (tc_ok) return launch_tc_prefill(*args, s);
   LA_REQUIRE(args->peer.num_peers == 0, LA_ERR_UNSUPPORTED,
              "la_prefill_fwd: the fused output gather needs the tensor-core kernel (%s)", why);
-  return launch_general_prefill(*args, s);
+  return general();
 }
 
 extern "C" int la_decode_fwd(const LaDecodeArgs* args, void* stream) {
@@ -145,9 +162,25 @@ extern "C" int la_decode_fwd(const LaDecodeArgs* args, void* stream) {
   if (args->num_seqs == 0) return LA_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const char* why = "";
+  if (args->slot_mapping != nullptr)
+    LA_REQUIRE(args->key != nullptr && args->value != nullptr, LA_ERR_INVALID_ARGUMENT,
+               "la_decode_fwd: slot_mapping given without the step's key / value rows");
+  // as in la_prefill_fwd: the general kernel leaves the cache write to a launch of its own
+  auto general = [&]() -> int {
+    const LaDecodeArgs& a = *args;
+    if (a.slot_mapping != nullptr) {
+      int wrc = write_cache_by_request(a.kv_dtype, a.q_dtype, a.query_start_loc, a.num_seqs, 1, 1, 0, a.key, a.value,
+                                       const_cast<void*>(a.k_cache), const_cast<void*>(a.v_cache), a.slot_mapping,
+                                       a.k_stride_t, a.k_stride_h, a.v_stride_t, a.v_stride_h, a.kc_stride_block,
+                                       a.kc_stride_head, a.vc_stride_block, a.vc_stride_head, a.num_kv_heads,
+                                       a.head_dim, a.block_size, a.x, a.k_scale, a.v_scale, s);
+      if (wrc != LA_OK) return wrc;
+    }
+    return launch_general_decode(a, s);
+  };
   if (args->kernel == LA_KERNEL_GENERAL) {
     LA_REQUIRE(args->peer.num_peers == 0, LA_ERR_UNSUPPORTED, "la_decode_fwd: the general kernel has no fused output gather");
-    return launch_general_decode(*args, s);
+    return general();
   }
   const bool fast_ok = fast_decode_supported(*args, &why);
   if (args->kernel == LA_KERNEL_TENSOR) {
@@ -158,7 +191,7 @@ extern "C" int la_decode_fwd(const LaDecodeArgs* args, void* stream) {
   if (fast_ok) return launch_fast_decode(*args, s);
   LA_REQUIRE(args->peer.num_peers == 0, LA_ERR_UNSUPPORTED,
              "la_decode_fwd: the fused output gather needs the split-KV kernel (%s)", why);
-  return launch_general_decode(*args, s);
+  return general();
 }
 
 extern "C" size_t la_prefill_workspace_bytes(const LaPrefillArgs* args) {

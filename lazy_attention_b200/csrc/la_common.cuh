@@ -103,6 +103,13 @@ bool tc_prefill_supported(const LaPrefillArgs& a, const char** why);
 size_t tc_prefill_workspace_bytes(const LaPrefillArgs& a);
 int launch_tc_prefill(const LaPrefillArgs& a, cudaStream_t stream);
 
+// Cache write of the tokens an attention call serves, as a launch of its own (la_meta.cu).
+int write_cache_by_request(int kv_dtype, int dtype, const int32_t* qsl, int batch, int max_q, int which,
+                           int skip_decode, const void* key, const void* value, void* kc, void* vc,
+                           const int64_t* slots, int64_t k_st, int64_t k_sh, int64_t v_st, int64_t v_sh, int64_t kc_sb,
+                           int64_t kc_sh, int64_t vc_sb, int64_t vc_sh, int Hkv, int D, int BS, int x,
+                           const float* ks, const float* vs, cudaStream_t s);
+
 // Split-KV decode (bulk-copy ring + mma).
 bool fast_decode_supported(const LaDecodeArgs& a, const char** why);
 size_t fast_decode_workspace_bytes(const LaDecodeArgs& a);

@@ -50,6 +50,11 @@ struct DecParams {
   int chunk_pages, n_splits, ignore_q_mask;
   float sm_scale;
   LaPeerOut peer;  // fused output gather: result rows go to every rank's buffer instead of `out`
+  // fused cache write of the new token's K/V row (slots == nullptr: off)
+  const void* key;
+  const void* value;
+  int64_t k_st, k_sh, v_st, v_sh;
+  const int64_t* slots;
   float* part_o;   // [num_seqs][Hq][n_splits][D]
   float* part_ml;  // [num_seqs][Hq][n_splits][2]
   int* status;
@@ -133,6 +138,29 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// n consecutive activations (BF16 or f16 bits) -> cache elements at dst: copied as they are for
+// a 16-bit cache, converted like la_write_paged_cache does (saturating fp8 of value / scale)
+// for an 8-bit one.
+template <int KV, bool BF16>
+__device__ __forceinline__ void to_cache_elems(const uint16_t* src, int n, uint8_t* dst, float scale) {
+  for (int i = 0; i < n; ++i) {
+    if constexpr (KV == 0) {
+      reinterpret_cast<uint16_t*>(dst)[i] = src[i];
+    } else {
+      float f;
+      if constexpr (BF16) f = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&src[i]));
+      else f = __half2float(*reinterpret_cast<const __half*>(&src[i]));
+      if constexpr (KV == 1) {
+        const __nv_fp8_e4m3 c(f / scale);
+        dst[i] = *reinterpret_cast<const uint8_t*>(&c);
+      } else {
+        const __nv_fp8_e5m2 c(f / scale);
+        dst[i] = *reinterpret_cast<const uint8_t*>(&c);
+      }
+    }
+  }
 }
 
 // One output element: to `out`, or with the fused gather to the same place of every rank's buffer.
@@ -338,6 +366,47 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
     if (!ok) break;
     const int pg = PPT * tl;
     const int np = min(PPT, n - pg);
+    if (p.slots != nullptr) {
+      // Fused cache write: the warp whose tile holds the sequence's last page puts the new
+      // token's K/V row (in cache format) into the landed copy of the page, so that this call
+      // attends to it, and into the page in global memory for the calls to come.
+      const int last = npages - 1 - (page0 + pg);  // index of the last page within this tile
+      if (last >= 0 && last < np) {
+        constexpr int X = 16 / Cfg::kElem;          // elements per 16-byte group
+        const int off_s = (seq_len - 1) & 15;
+        const int64_t slot = p.slots[row_q];
+        uint8_t* kp_s = const_cast<uint8_t*>(tile) + last * Cfg::kPageBytes;
+        uint8_t* vp_s = const_cast<uint8_t*>(tile) + (PPT + last) * Cfg::kPageBytes;
+        uint8_t* kp_g = nullptr;
+        uint8_t* vp_g = nullptr;
+        int off_g = 0;
+        if (slot >= 0) {
+          const int64_t blk = slot >> 4;
+          off_g = (int)(slot & 15);
+          kp_g = const_cast<uint8_t*>(p.kc) + blk * p.kc_sb + (int64_t)kvh * p.kc_sh;
+          vp_g = const_cast<uint8_t*>(p.vc) + blk * p.vc_sb + (int64_t)kvh * p.vc_sh;
+        }
+        const uint16_t* krow = reinterpret_cast<const uint16_t*>(p.key) + (int64_t)row_q * p.k_st + (int64_t)kvh * p.k_sh;
+        const uint16_t* vrow = reinterpret_cast<const uint16_t*>(p.value) + (int64_t)row_q * p.v_st + (int64_t)kvh * p.v_sh;
+        const float ksc = (KV != 0 && p.k_scale) ? *p.k_scale : 1.f;
+        const float vsc = (KV != 0 && p.v_scale) ? *p.v_scale : 1.f;
+        for (int g = lane; g < D / X; g += 32) {      // K page [D/X][16][X]
+          uint8_t grp[16];
+          to_cache_elems<KV, BF16>(krow + g * X, X, grp, ksc);
+          *reinterpret_cast<uint4*>(kp_s + (g * 16 + off_s) * 16) = *reinterpret_cast<const uint4*>(grp);
+          if (kp_g) *reinterpret_cast<uint4*>(kp_g + (g * 16 + off_g) * 16) = *reinterpret_cast<const uint4*>(grp);
+        }
+        for (int d = lane; d < D; d += 32) {          // V page [D][16]
+          uint8_t el[2];
+          to_cache_elems<KV, BF16>(vrow + d, 1, el, vsc);
+          for (int bb = 0; bb < Cfg::kElem; ++bb) {
+            vp_s[(d * 16 + off_s) * Cfg::kElem + bb] = el[bb];
+            if (vp_g) vp_g[(d * 16 + off_g) * Cfg::kElem + bb] = el[bb];
+          }
+        }
+        __syncwarp();
+      }
+    }
     float s[PPT][4];
     bool vlo[PPT], vhi[PPT];
 #pragma unroll
@@ -691,6 +760,8 @@ int launch_fast_decode(const LaDecodeArgs& a, cudaStream_t stream) {
   p.qsl = a.query_start_loc; p.seq_lens = a.seq_lens; p.is_lazy = a.is_lazy;
   p.k_scale = a.k_scale; p.v_scale = a.v_scale;
   p.peer = a.peer;
+  p.key = a.key; p.value = a.value; p.slots = a.slot_mapping;
+  p.k_st = a.k_stride_t; p.k_sh = a.k_stride_h; p.v_st = a.v_stride_t; p.v_sh = a.v_stride_h;
   p.cs = a.cos_sin_cache; p.cs_rows = a.cos_sin_rows;
   p.Hq = a.num_q_heads; p.Hkv = a.num_kv_heads; p.G = a.num_q_heads / a.num_kv_heads;
   p.chunk_pages = pl.chunk_pages; p.n_splits = pl.n_splits; p.ignore_q_mask = a.ignore_q_mask;

@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(kThreads) general_kernel(GenParams p) {
         int rot = 0;
         if (j < ctx_pages) {
           int pad = 0;
-          if (mode == kDecodeLazy) {
+          if (mode == kDecodeLazy || (p.packed != nullptr && mode != kDecodeMepic)) {
             const int64_t pk = p.packed[(int64_t)b * p.packed_stride + j];
             blk = (int)(pk >> 32);
             rot = (int)((pk >> 16) & 0xFFFF);
@@ -415,6 +415,7 @@ int launch_general_prefill(const LaPrefillArgs& a, cudaStream_t stream) {
   p.vc_sb = a.vc_stride_block; p.vc_sh = a.vc_stride_head;
   p.block_table = a.block_table; p.q_offset = a.q_offset; p.q_mask = a.q_mask;
   p.table_stride = a.table_stride;
+  p.packed = a.packed_block_table; p.packed_stride = a.packed_stride;
   p.qsl = a.query_start_loc; p.seq_lens = a.seq_lens; p.is_lazy = a.is_lazy;
   p.k_scale = a.k_scale; p.v_scale = a.v_scale;
   p.cs = a.cos_sin_cache; p.cs_rows = a.cos_sin_rows; p.cs_dtype = a.cos_sin_dtype;

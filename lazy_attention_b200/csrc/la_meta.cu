@@ -56,13 +56,14 @@ __device__ __forceinline__ CT to_cache(T v, float scale) {
   }
 }
 
+// One token's K and V rows into the caches (all threads of the block take part).
 template <typename T, typename CT>
-__global__ void write_cache_kernel(const T* __restrict__ key, const T* __restrict__ value, CT* __restrict__ kc,
-                                   CT* __restrict__ vc, const int64_t* __restrict__ slots, int64_t k_st,
-                                   int64_t k_sh, int64_t v_st, int64_t v_sh, int64_t kc_sb, int64_t kc_sh,
-                                   int64_t vc_sb, int64_t vc_sh, int Hkv, int D, int BS, int x,
-                                   const float* k_scale, const float* v_scale) {
-  const int64_t tok = blockIdx.x;
+__device__ __forceinline__ void write_token(int64_t tok, const T* __restrict__ key, const T* __restrict__ value,
+                                            CT* __restrict__ kc, CT* __restrict__ vc,
+                                            const int64_t* __restrict__ slots, int64_t k_st, int64_t k_sh,
+                                            int64_t v_st, int64_t v_sh, int64_t kc_sb, int64_t kc_sh,
+                                            int64_t vc_sb, int64_t vc_sh, int Hkv, int D, int BS, int x,
+                                            const float* k_scale, const float* v_scale) {
   const int64_t slot = slots[tok];
   if (slot < 0) return;  // padding token
   const int64_t blk = slot / BS;
@@ -78,6 +79,37 @@ __global__ void write_cache_kernel(const T* __restrict__ key, const T* __restric
         to_cache<T, CT>(kv, ik);
     vc[blk * vc_sb + (int64_t)h * vc_sh + (int64_t)d * BS + off] = to_cache<T, CT>(vv, iv);
   }
+}
+
+template <typename T, typename CT>
+__global__ void write_cache_kernel(const T* __restrict__ key, const T* __restrict__ value, CT* __restrict__ kc,
+                                   CT* __restrict__ vc, const int64_t* __restrict__ slots, int64_t k_st,
+                                   int64_t k_sh, int64_t v_st, int64_t v_sh, int64_t kc_sb, int64_t kc_sh,
+                                   int64_t vc_sb, int64_t vc_sh, int Hkv, int D, int BS, int x,
+                                   const float* k_scale, const float* v_scale) {
+  write_token<T, CT>(blockIdx.x, key, value, kc, vc, slots, k_st, k_sh, v_st, v_sh, kc_sb, kc_sh, vc_sb, vc_sh, Hkv,
+                     D, BS, x, k_scale, v_scale);
+}
+
+// The same for the tokens of the requests an attention call serves: block (i, b) takes token
+// i of request b.  which = 0: requests with more than one query token, or all when
+// skip_decode is off (what the prefill call serves); which = 1: requests with exactly one
+// query token (what the decode call serves).
+template <typename T, typename CT>
+__global__ void write_cache_by_request_kernel(const int32_t* __restrict__ qsl, int which, int skip_decode,
+                                              const T* __restrict__ key, const T* __restrict__ value,
+                                              CT* __restrict__ kc, CT* __restrict__ vc,
+                                              const int64_t* __restrict__ slots, int64_t k_st, int64_t k_sh,
+                                              int64_t v_st, int64_t v_sh, int64_t kc_sb, int64_t kc_sh,
+                                              int64_t vc_sb, int64_t vc_sh, int Hkv, int D, int BS, int x,
+                                              const float* k_scale, const float* v_scale) {
+  const int b = blockIdx.y;
+  const int s0 = qsl[b], qlen = qsl[b + 1] - s0;
+  if ((int)blockIdx.x >= qlen) return;
+  if (which == 0 && skip_decode && qlen == 1) return;
+  if (which == 1 && qlen != 1) return;
+  write_token<T, CT>(s0 + blockIdx.x, key, value, kc, vc, slots, k_st, k_sh, v_st, v_sh, kc_sb, kc_sh, vc_sb, vc_sh,
+                     Hkv, D, BS, x, k_scale, v_scale);
 }
 
 template <typename T, typename CT>
@@ -101,7 +133,61 @@ int launch_write_t(const LaWriteCacheArgs& a, cudaStream_t s) {
   return LA_ERR_UNSUPPORTED;
 }
 
+template <typename T, typename CT>
+int launch_by_request(const int32_t* qsl, int batch, int max_q, int which, int skip_decode, const void* key,
+                      const void* value, void* kc, void* vc, const int64_t* slots, int64_t k_st, int64_t k_sh,
+                      int64_t v_st, int64_t v_sh, int64_t kc_sb, int64_t kc_sh, int64_t vc_sb, int64_t vc_sh, int Hkv,
+                      int D, int BS, int x, const float* ks, const float* vs, cudaStream_t s) {
+  dim3 grid((unsigned)max_q, (unsigned)batch);
+  write_cache_by_request_kernel<T, CT><<<grid, 256, 0, s>>>(qsl, which, skip_decode, (const T*)key, (const T*)value,
+                                                            (CT*)kc, (CT*)vc, slots, k_st, k_sh, v_st, v_sh, kc_sb,
+                                                            kc_sh, vc_sb, vc_sh, Hkv, D, BS, x, ks, vs);
+  count_launch();
+  LA_CHECK_CUDA(cudaGetLastError());
+  return LA_OK;
+}
+
+template <typename T>
+int launch_by_request_t(int kv_dtype, int dtype, const int32_t* qsl, int batch, int max_q, int which, int skip_decode,
+                        const void* key, const void* value, void* kc, void* vc, const int64_t* slots, int64_t k_st,
+                        int64_t k_sh, int64_t v_st, int64_t v_sh, int64_t kc_sb, int64_t kc_sh, int64_t vc_sb,
+                        int64_t vc_sh, int Hkv, int D, int BS, int x, const float* ks, const float* vs,
+                        cudaStream_t s) {
+#define LA_BY_REQ(CT)                                                                                              \
+  return launch_by_request<T, CT>(qsl, batch, max_q, which, skip_decode, key, value, kc, vc, slots, k_st, k_sh, v_st, \
+                                  v_sh, kc_sb, kc_sh, vc_sb, vc_sh, Hkv, D, BS, x, ks, vs, s)
+  if (kv_dtype == dtype) LA_BY_REQ(T);
+  if (kv_dtype == LA_DTYPE_FP8_E4M3) LA_BY_REQ(__nv_fp8_e4m3);
+  if (kv_dtype == LA_DTYPE_FP8_E5M2) LA_BY_REQ(__nv_fp8_e5m2);
+#undef LA_BY_REQ
+  set_error("fused cache write: cache dtype %d with activation dtype %d unsupported", kv_dtype, dtype);
+  return LA_ERR_UNSUPPORTED;
+}
+
 }  // namespace
+
+// Cache write of the tokens an attention call serves, as a launch of its own: used where
+// the attention kernel that was selected does not write the rows itself.
+int write_cache_by_request(int kv_dtype, int dtype, const int32_t* qsl, int batch, int max_q, int which,
+                           int skip_decode, const void* key, const void* value, void* kc, void* vc,
+                           const int64_t* slots, int64_t k_st, int64_t k_sh, int64_t v_st, int64_t v_sh, int64_t kc_sb,
+                           int64_t kc_sh, int64_t vc_sb, int64_t vc_sh, int Hkv, int D, int BS, int x,
+                           const float* ks, const float* vs, cudaStream_t s) {
+  if (batch <= 0 || max_q <= 0) return LA_OK;
+#define LA_BY_REQ_T(T)                                                                                             \
+  return launch_by_request_t<T>(kv_dtype, dtype, qsl, batch, max_q, which, skip_decode, key, value, kc, vc, slots,  \
+                                k_st, k_sh, v_st, v_sh, kc_sb, kc_sh, vc_sb, vc_sh, Hkv, D, BS, x, ks, vs, s)
+  switch (dtype) {
+    case LA_DTYPE_F32: LA_BY_REQ_T(float);
+    case LA_DTYPE_F16: LA_BY_REQ_T(__half);
+    case LA_DTYPE_BF16: LA_BY_REQ_T(__nv_bfloat16);
+    default: break;
+  }
+#undef LA_BY_REQ_T
+  set_error("fused cache write: activation dtype %d unsupported", dtype);
+  return LA_ERR_UNSUPPORTED;
+}
+
 }  // namespace la
 
 extern "C" int la_write_paged_cache(const LaWriteCacheArgs* args, void* stream) {

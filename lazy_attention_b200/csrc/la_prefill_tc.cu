@@ -74,6 +74,8 @@ struct TcParams {
   const int32_t* q_offset;
   const int32_t* q_mask;
   int64_t table_stride;
+  const int64_t* packed;  // optional: block << 32 | q_offset << 16 | q_mask per page
+  int64_t packed_stride;
   const int32_t* qsl;
   const int32_t* seq_lens;
   const uint8_t* is_lazy;
@@ -85,6 +87,11 @@ struct TcParams {
   int64_t kc_sb, kc_sh, vc_sb, vc_sh, num_blocks;
   const float* k_scale;
   const float* v_scale;
+  // fused cache write: slots of the new tokens (nullptr = off), the caches as writable bytes
+  const int64_t* slots;
+  uint8_t* kcw;
+  uint8_t* vcw;
+  int64_t kcw_sb, kcw_sh, vcw_sb, vcw_sh;  // bytes
   LaPeerOut peer;  // fused output gather: result rows go to every rank's buffer instead of `out`
   int Hq, Hkv, G, g_shift;
   int rot_mode, is_mepic, skip_decode, n_splits, page_ratio;
@@ -108,6 +115,10 @@ __device__ __forceinline__ float ex2_pure(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+
+// Tensor-memory column (relative to the row tile's S columns) of the P chunk for keys
+// [32c, 32c+32): keys 0..63 over S columns 0..31, keys 64..127 over S columns 96..127.
+__device__ __forceinline__ constexpr int p_col(int c) { return c < 2 ? c * 16 : 96 + (c - 2) * 16; }
 
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
@@ -291,6 +302,61 @@ __device__ __forceinline__ void rotate_chunk_f16(uint4& a, uint4& b, const uint4
   }
 }
 
+// Fused cache write: 8 consecutive dims [d0, d0+8) of a new token's K (V) row, given in the
+// activation dtype, into slot `off` of page `blk` -- the element placement and the fp8
+// conversion (saturating, of value / scale) of la_write_paged_cache.
+template <bool BF16, int KVF8>
+__device__ __forceinline__ void cache_put_k(const TcParams& p, int64_t blk, int off, int kvh, int d0, uint4 v,
+                                            float scale) {
+  uint8_t* page = p.kcw + blk * p.kcw_sb + (int64_t)kvh * p.kcw_sh;
+  if constexpr (KVF8 == 0) {
+    *reinterpret_cast<uint4*>(page + ((d0 >> 3) * 16 + off) * 16) = v;  // [D/8][16][8] x 2 bytes
+  } else {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
+    uint8_t o[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = unpack2<BF16>(w[i]);
+      if constexpr (KVF8 == 1) {
+        const __nv_fp8_e4m3 a(f.x / scale), b(f.y / scale);
+        o[2 * i] = *reinterpret_cast<const uint8_t*>(&a);
+        o[2 * i + 1] = *reinterpret_cast<const uint8_t*>(&b);
+      } else {
+        const __nv_fp8_e5m2 a(f.x / scale), b(f.y / scale);
+        o[2 * i] = *reinterpret_cast<const uint8_t*>(&a);
+        o[2 * i + 1] = *reinterpret_cast<const uint8_t*>(&b);
+      }
+    }
+    // [D/16][16][16] x 1 byte: 8 dims are half of a 16-byte group
+    *reinterpret_cast<uint2*>(page + ((d0 >> 4) * 16 + off) * 16 + (d0 & 15)) = *reinterpret_cast<const uint2*>(o);
+  }
+}
+template <bool BF16, int KVF8>
+__device__ __forceinline__ void cache_put_v(const TcParams& p, int64_t blk, int off, int kvh, int d0, uint4 v,
+                                            float scale) {
+  uint8_t* page = p.vcw + blk * p.vcw_sb + (int64_t)kvh * p.vcw_sh;  // [D][16]
+  if constexpr (KVF8 == 0) {
+    const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
+#pragma unroll
+    for (int x = 0; x < 8; ++x) *reinterpret_cast<uint16_t*>(page + ((d0 + x) * 16 + off) * 2) = e[x];
+  } else {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = unpack2<BF16>(w[i]);
+      if constexpr (KVF8 == 1) {
+        const __nv_fp8_e4m3 a(f.x / scale), b(f.y / scale);
+        page[(d0 + 2 * i) * 16 + off] = *reinterpret_cast<const uint8_t*>(&a);
+        page[(d0 + 2 * i + 1) * 16 + off] = *reinterpret_cast<const uint8_t*>(&b);
+      } else {
+        const __nv_fp8_e5m2 a(f.x / scale), b(f.y / scale);
+        page[(d0 + 2 * i) * 16 + off] = *reinterpret_cast<const uint8_t*>(&a);
+        page[(d0 + 2 * i + 1) * 16 + off] = *reinterpret_cast<const uint8_t*>(&b);
+      }
+    }
+  }
+}
+
 // PAIR: two CTAs of a cluster run every MMA together (M = 256, 128 rows of each row tile
 // per CTA).  Each CTA then holds only half of every K tile (64 of its 128 keys) and half of
 // every V tile (64 of the D dims of all 128 keys), so a stage is half as large and the ring
@@ -354,9 +420,19 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
   const int j0 = (int)((int64_t)total * split / p.n_splits);
   const int j1 = (int)((int64_t)total * (split + 1) / p.n_splits);
   const bool lazy = (p.rot_mode == LA_ROT_MEPIC) ? true : (p.is_lazy != nullptr && p.is_lazy[b] != 0);
-  const int32_t* bt_row = p.block_table + (int64_t)b * p.table_stride;
+  // Per-page metadata: one 8-byte entry of the packed table when the caller has one,
+  // else the three int32 tables (which share one row stride).
+  const int64_t* pk_row = p.packed ? p.packed + (int64_t)b * p.packed_stride : nullptr;
+  const int32_t* bt_row = p.block_table ? p.block_table + (int64_t)b * p.table_stride : nullptr;
   const int32_t* off_row = p.q_offset ? p.q_offset + (int64_t)b * p.table_stride : nullptr;
   const int32_t* msk_row = p.q_mask ? p.q_mask + (int64_t)b * p.table_stride : nullptr;
+  auto page_block = [&](int page) -> int { return pk_row ? (int)(pk_row[page] >> 32) : bt_row[page]; };
+  auto page_offset = [&](int page) -> int {
+    return pk_row ? (int)((pk_row[page] >> 16) & 0xFFFF) : (off_row ? off_row[page] : 0);
+  };
+  auto page_pad = [&](int page) -> int {
+    return pk_row ? (int)(pk_row[page] & 0xFFFF) : (msk_row ? msk_row[page] : 0);
+  };
 
   // Barriers the MMA-issuing thread waits on collect the arrivals of both CTAs of a pair
   // (they live in the pair's first CTA, the only one that issues MMAs); the barriers the MMA
@@ -412,9 +488,10 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
   if (warp < kWarpStage) {
     // =============================== softmax ===============================
     // One thread per score row.  The row's 128 scores of a tile are consumed in four
-    // 32-column chunks: while chunk c is scaled, exponentiated and packed, the
-    // tensor-memory load of chunk c+1 is already in flight.  P (two keys per column)
-    // is written over S columns 0..63, always behind the columns still to be read.
+    // 32-column chunks: while one chunk is scaled, exponentiated and packed, the
+    // tensor-memory load of the next is already in flight.  P (two keys per column) is
+    // written over S columns that have been read: keys 0..63 over columns 0..31, keys
+    // 64..127 over columns 96..127 (see p_col).
     const int t = warp >> 2;          // row tile
     const int qd = warp & 3;          // lane quarter of tensor memory this warp may touch
     const int r = qd * 32 + lane;     // row within the tile
@@ -454,7 +531,7 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
         const int page = j * kPagesPerTile + lane;
         v = 0;
         if (page < ctx_pages) {
-          const int pad = (lazy && msk_row) ? msk_row[page] : 0;
+          const int pad = lazy ? page_pad(page) : 0;
           v = min(ctx, (page + 1) * 16 - pad) - page * 16;
           v = max(0, min(16, v));
         }
@@ -513,14 +590,14 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
 #pragma unroll 1
         for (int pc = 0; pc < c; ++pc) {  // P chunks of this tile formed with the old maximum
           uint32_t pp[16];
-          tmem_ld16(tS + pc * 16, pp);
+          tmem_ld16(tS + p_col(pc), pp);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float2 f = unpack2<MB>(pp[i]);
             pp[i] = pack2<MB>(f.x * alpha, f.y * alpha);
           }
-          tmem_st16(tS + pc * 16, pp);
+          tmem_st16(tS + p_col(pc), pp);
         }
         tmem_st_wait();
       }
@@ -551,7 +628,7 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
         }
       }
       l_sum += (acc_a.x + acc_a.y) + (acc_b.x + acc_b.y);
-      tmem_st16(tS + c * 16, pk);
+      tmem_st16(tS + p_col(c), pk);
     };
     int vc_next = page_valid(j0);
     for (int j = j0; j < j1 && ok; ++j) {
@@ -582,9 +659,6 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
         mx_a = fmaxf(mx_a, row_max32(sa));
         mx_b = fmaxf(mx_b, row_max32(sb));
         const float m_tile = fmaxf(mx_a, mx_b) * scale_log2;
-        // the first two chunks are fetched again while the decision is taken
-        tmem_ld32(tS, sa);
-        tmem_ld32(tS + 32, sb);
         LA_STAMP(t * 8 + 1, j - j0);
         float alpha = 1.f;
         if (j == j0) {
@@ -597,7 +671,6 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
           // rare: bring the accumulator row and the row sum to the new maximum
           l_sum *= alpha;
           if (j != j0) {
-            tmem_ld_wait();
 #pragma unroll 1
             for (int oc = 0; oc < D / 32; ++oc) {
               uint32_t o[32];
@@ -608,15 +681,14 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
               tmem_st32(tO + oc * 32, o);
             }
             tmem_st_wait();
-            tmem_ld32(tS, sa);
-            tmem_ld32(tS + 32, sb);
           }
         }
-        // Pass B: exponentials and P, one straight-line block for the four chunks.
-        // bf16 P is formed by truncation of e * (1 + 2^-9) (the factor rides on the
-        // subtracted maximum), which is unbiased like rounding and costs one byte
-        // permute per pair instead of two integer adds and a permute; the row sum is
-        // taken from the same values and scaled back by 1 / (1 + 2^-9).
+        // Pass B: exponentials and P, one straight-line block for the four chunks, starting
+        // with chunks 2 and 3, which pass A left in registers, while chunks 0 and 1 are
+        // fetched again.  bf16 P is formed by truncation of e * (1 + 2^-9) (the factor rides
+        // on the subtracted maximum), which is unbiased like rounding and costs one byte
+        // permute per pair instead of two integer adds and a permute; the row sum is taken
+        // from the same values and scaled back by 1 / (1 + 2^-9).
         constexpr float kBiasLog2 = MB ? 0.0028151247f : 0.f;       // log2(1 + 2^-9)
         constexpr float kUnbias = MB ? 0.998050682f : 1.f;          // 1 / (1 + 2^-9)
         const float neg_m = ((m_used == -INFINITY) ? 0.f : -m_used) + kBiasLog2;
@@ -635,21 +707,19 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
               pk[i >> 1] = pack2<false>(e.x, e.y);
             }
           }
-          tmem_st16(tS + c * 16, pk);
+          tmem_st16(tS + p_col(c), pk);
         };
-        tmem_ld_wait_for(sa);
-        tie_after_wait(sb);
-        exp_chunk(sa, 0);
-        tmem_ld32(tS + 64, sa);
-        LA_STAMP(t * 8 + 2, j - j0);
-        exp_chunk(sb, 1);
-        tmem_ld_wait_for(sa);
-        tmem_ld32(tS + 96, sb);
-        LA_STAMP(t * 8 + 3, j - j0);
         exp_chunk(sa, 2);
+        tmem_ld32(tS, sa);
+        LA_STAMP(t * 8 + 2, j - j0);
+        exp_chunk(sb, 3);
+        tmem_ld_wait_for(sa);
+        tmem_ld32(tS + 32, sb);
+        LA_STAMP(t * 8 + 3, j - j0);
+        exp_chunk(sa, 0);
         tmem_ld_wait_for(sb);
         LA_STAMP(t * 8 + 4, j - j0);
-        exp_chunk(sb, 3);
+        exp_chunk(sb, 1);
         LA_STAMP(t * 8 + 5, j - j0);
         l_sum = fmaf((acc_a.x + acc_a.y) + (acc_b.x + acc_b.y), kUnbias, l_sum);
         tmem_st_wait();
@@ -671,9 +741,9 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
       LA_STAMP(t * 8 + 3, j - j0);
       tmem_ld_wait();
       tmem_ld32(tS + 96, sb);
+      tmem_ld_wait();  // P of chunk 2 goes over the columns of chunk 3: have chunk 3 in registers first
       do_chunk(sa, 2, j, self, tile_full, vc, n0, scale_log2);
       LA_STAMP(t * 8 + 4, j - j0);
-      tmem_ld_wait();
       do_chunk(sb, 3, j, self, tile_full, vc, n0, scale_log2);
       LA_STAMP(t * 8 + 5, j - j0);
       tmem_st_wait();
@@ -752,6 +822,11 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
     const int i = tid - kWarpStage * 32;  // 0..127
     bool ok = true;
     const uint8_t* cs = reinterpret_cast<const uint8_t*>(p.cs);
+    // Fused cache write: the unit that holds the request's last row stages every new-token
+    // tile of the request (each tile in exactly one of its splits) and stores the raw rows.
+    const bool put = p.slots != nullptr && row0_pair + kRowsPerUnit >= nrows;
+    const float put_ks = (KVF8 != 0 && p.k_scale) ? *p.k_scale : 1.f;
+    const float put_vs = (KVF8 != 0 && p.v_scale) ? *p.v_scale : 1.f;
     // fp8 caches: asynchronous copies of tile jn's raw pages into its operand stage
     // (after the stage's previous tile was consumed).  One commit group per call,
     // also when there is nothing to copy, so that the group count stays uniform.
@@ -762,7 +837,7 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
         if (un > 0) good = mbar_wait(&bar_k_empty[stn], (uint32_t)(un - 1) & 1u, p.status, 204);
         const int page = jn * kPagesPerTile + (i >> 4);
         if (good && page < ctx_pages) {
-          int64_t blk = bt_row[page];
+          int64_t blk = page_block(page);
           if (blk < 0 || blk >= p.num_blocks) blk = 0;
           const uint8_t* src = p.kc + blk * p.kc_sb + (int64_t)kvh * p.kc_sh + (i & 15) * 16;
           const uint32_t dst = smem_u32(sK + stn * Cfg::kTileBytes + (i >> 3) * Cfg::kRowGroupBytes + (i & 7) * 16);
@@ -785,7 +860,7 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
             const int idx = i + it * 128;
             const int pg = idx / D, d = idx - pg * D;
             if (pg < npages) {
-              int64_t vb = bt_row[jn * kPagesPerTile + pg];
+              int64_t vb = page_block(jn * kPagesPerTile + pg);
               if (vb < 0 || vb >= p.num_blocks) vb = 0;
               cp_async_16(smem_u32(sV + stn * Cfg::kTileBytes + pg * Cfg::kPageBytes + (d >> 3) * 256 + (d & 7) * 16),
                           p.vc + vb * p.vc_sb + (int64_t)kvh * p.vc_sh + d * 16);
@@ -803,7 +878,7 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
     // rotation entry of this thread's page, read one tile ahead of its use
     auto page_rot = [&](int jn) -> int {
       const int pg = jn * kPagesPerTile + (i >> 4);
-      return (lazy && off_row && jn < j1 && pg < ctx_pages) ? off_row[pg] : 0;
+      return (lazy && jn < j1 && pg < ctx_pages) ? page_offset(pg) : 0;
     };
     int rot_next = KVF8 != 0 ? page_rot(j0) : 0;
     for (int j = j0; j < j1 && ok; ++j) {
@@ -822,7 +897,7 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
           const int page = j * kPagesPerTile + 4 * (int)cta_rank + (key >> 4);
           int pos = 0;
           if (lazy && page < ctx_pages) {
-            const int rot = off_row ? off_row[page] : 0;
+            const int rot = page_offset(page);
             if (p.rot_mode == LA_ROT_LAZY) {
               pos = rot != 0 ? rot - 1 : 0;
             } else {
@@ -874,6 +949,13 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
               if (present) {
                 a = *reinterpret_cast<const uint4*>(krow + (g0 + g) * 16);
                 bq = *reinterpret_cast<const uint4*>(krow + (g0 + g + NCH / 2) * 16);
+                if (put) {
+                  const int64_t slot = p.slots[s0 + n];
+                  if (slot >= 0) {
+                    cache_put_k<BF16, KVF8>(p, slot >> 4, (int)(slot & 15), kvh, (g0 + g) * 8, a, put_ks);
+                    cache_put_k<BF16, KVF8>(p, slot >> 4, (int)(slot & 15), kvh, (g0 + g + NCH / 2) * 8, bq, put_ks);
+                  }
+                }
                 if (pos > 0) {
                   const uint4 cvv = __ldg(reinterpret_cast<const uint4*>(crow + (g0 + g) * 16));
                   const uint4 svv = __ldg(reinterpret_cast<const uint4*>(crow + D + (g0 + g) * 16));
@@ -898,7 +980,14 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
 #pragma unroll 2
             for (int g = 0; g < NCH / 2; ++g) {
               uint4 val = make_uint4(0, 0, 0, 0);
-              if (presentv) val = *reinterpret_cast<const uint4*>(vrow + g * 16);
+              if (presentv) {
+                val = *reinterpret_cast<const uint4*>(vrow + g * 16);
+                if (put) {
+                  const int64_t slot = p.slots[s0 + nv];
+                  if (slot >= 0)
+                    cache_put_v<BF16, KVF8>(p, slot >> 4, (int)(slot & 15), kvh, (int)cta_rank * (D / 2) + g * 8, val, put_vs);
+                }
+              }
               const uint16_t* e = reinterpret_cast<const uint16_t*>(&val);
 #pragma unroll
               for (int x = 0; x < 8; ++x) *reinterpret_cast<uint16_t*>(base + g * 256 + x * 16) = e[x];
@@ -1041,6 +1130,13 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
             if (present) {
               a = *reinterpret_cast<const uint4*>(krow + g * 16);
               bq = *reinterpret_cast<const uint4*>(krow + (g + NCH / 2) * 16);
+              if (put) {
+                const int64_t slot = p.slots[s0 + n];
+                if (slot >= 0) {
+                  cache_put_k<BF16, KVF8>(p, slot >> 4, (int)(slot & 15), kvh, g * 8, a, put_ks);
+                  cache_put_k<BF16, KVF8>(p, slot >> 4, (int)(slot & 15), kvh, (g + NCH / 2) * 8, bq, put_ks);
+                }
+              }
               if (pos > 0) {
                 const uint4 cv = __ldg(reinterpret_cast<const uint4*>(crow + g * 16));
                 const uint4 sv = __ldg(reinterpret_cast<const uint4*>(crow + D + g * 16));
@@ -1069,6 +1165,10 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
             uint4 val = make_uint4(0, 0, 0, 0);
             if (present) {
               val = *reinterpret_cast<const uint4*>(vrow + g * 16);
+              if (put) {
+                const int64_t slot = p.slots[s0 + n];
+                if (slot >= 0) cache_put_v<BF16, KVF8>(p, slot >> 4, (int)(slot & 15), kvh, g * 8, val, put_vs);
+              }
               if constexpr (KVF8 != 0) val = to_f16x8_scaled<BF16>(val, inv_out_scale);
             }
             const uint16_t* e = reinterpret_cast<const uint16_t*>(&val);
@@ -1101,22 +1201,26 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
         if (!issuer) return;
         const uint32_t qa = smem_u32(sQ) + t * (128 * D * 2);
         const uint32_t ka = smem_u32(sK) + st * Cfg::kKStageBytes;
+        // descriptors of the first k-step; a k-step of 16 elements is 256 bytes further on
+        // (the start-address field counts 16-byte units)
+        const uint64_t da0 = smem_desc_nosw(qa, 128, Cfg::kRowGroupBytes);
+        const uint64_t db0 = smem_desc_nosw(ka, 128, Cfg::kRowGroupBytes);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint64_t da = smem_desc_nosw(qa + ks * 256, 128, Cfg::kRowGroupBytes);
-          const uint64_t db = smem_desc_nosw(ka + ks * 256, 128, Cfg::kRowGroupBytes);
-          if constexpr (PAIR) mma_ss_pair(tmem + t * 128, da, db, idesc_qk, ks > 0);
-          else mma_ss(tmem + t * 128, da, db, idesc_qk, ks > 0);
+          if constexpr (PAIR) mma_ss_pair(tmem + t * 128, da0 + ks * 16, db0 + ks * 16, idesc_qk, ks > 0);
+          else mma_ss(tmem + t * 128, da0 + ks * 16, db0 + ks * 16, idesc_qk, ks > 0);
         }
         commit(&bar_s_full[t]);
       };
       auto issue_pv = [&](int t, int st, int npages, bool first) {
         if (!issuer) return;
         const uint32_t va = smem_u32(sV) + st * Cfg::kVStageBytes;
+        const uint64_t db0 = smem_desc_nosw(va, 128, 256);
         for (int pg = 0; pg < npages; ++pg) {
-          const uint64_t db = smem_desc_nosw(va + pg * Cfg::kVPageBytes, 128, 256);
-          if constexpr (PAIR) mma_ts_pair(tmem + 256 + t * 128, tmem + t * 128 + pg * 8, db, idesc_pv, !(first && pg == 0));
-          else mma_ts(tmem + 256 + t * 128, tmem + t * 128 + pg * 8, db, idesc_pv, !(first && pg == 0));
+          const uint64_t db = db0 + (uint64_t)(pg * (Cfg::kVPageBytes >> 4));
+          const uint32_t pa = tmem + t * 128 + (pg < 4 ? pg * 8 : 96 + (pg - 4) * 8);  // see p_col
+          if constexpr (PAIR) mma_ts_pair(tmem + 256 + t * 128, pa, db, idesc_pv, !(first && pg == 0));
+          else mma_ts(tmem + 256 + t * 128, pa, db, idesc_pv, !(first && pg == 0));
         }
       };
       if (ok) {
@@ -1179,7 +1283,7 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
       const int st = (j - j0) % KS, u = (j - j0) / KS;
       const int npages = min(kPagesPerTile, ctx_pages - j * kPagesPerTile);
       int coord = 0;
-      if (lane < npages) coord = bt_row[j * kPagesPerTile + lane] * p.page_ratio + kvh;
+      if (lane < npages) coord = page_block(j * kPagesPerTile + lane) * p.page_ratio + kvh;
       if (u > 0) ok = mbar_wait(&bar_k_empty[st], (uint32_t)(u - 1) & 1u, p.status, 401);
       if (!ok) break;
       if constexpr (PAIR) {
@@ -1555,6 +1659,16 @@ int launch_tc_with_scratch(const LaPrefillArgs& a, cudaStream_t stream, void* sc
   p.o_st = a.o_stride_t; p.o_sh = a.o_stride_h;
   p.block_table = a.block_table; p.q_offset = a.q_offset; p.q_mask = a.q_mask;
   p.table_stride = a.table_stride;
+  p.packed = a.packed_block_table; p.packed_stride = a.packed_stride;
+  p.slots = a.slot_mapping;
+  {
+    const int64_t e = a.kv_dtype == a.q_dtype ? 2 : 1;  // bytes per cache element
+    p.kcw = reinterpret_cast<uint8_t*>(const_cast<void*>(a.k_cache));
+    p.vcw = reinterpret_cast<uint8_t*>(const_cast<void*>(a.v_cache));
+    p.kcw_sb = a.kc_stride_block * e; p.kcw_sh = a.kc_stride_head * e;
+    p.vcw_sb = a.vc_stride_block * e; p.vcw_sh = a.vc_stride_head * e;
+    if (a.slot_mapping != nullptr) { p.k_scale = a.k_scale; p.v_scale = a.v_scale; }
+  }
   p.qsl = a.query_start_loc; p.seq_lens = a.seq_lens; p.is_lazy = a.is_lazy;
   p.cs = a.cos_sin_cache; p.cs_rows = a.cos_sin_rows;
   p.Hq = a.num_q_heads; p.Hkv = a.num_kv_heads; p.G = a.num_q_heads / a.num_kv_heads;

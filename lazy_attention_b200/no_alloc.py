@@ -54,41 +54,13 @@ def context_attention_fwd_no_alloc(*args, **kwargs) -> None:
 def _build_args(q, k, v, o, k_cache, v_cache, b_loc, b_start_loc, b_seq_len,
                 max_seq_len, max_input_len, cos_sin_cache=None, is_lazy=None,
                 q_offset=None, q_mask=None, sm_scale=None, skip_decode=False,
-                rot_mode: int = _lib.ROT_LAZY, is_mepic: bool = False):
-    for t in (q, k, v, o, k_cache, v_cache, b_loc, b_start_loc, b_seq_len):
-        if not t.is_cuda:
-            raise RuntimeError("lazy_attention_b200 runs on CUDA tensors only (no CPU path)")
-    if q.dtype not in _ACT or not (k.dtype == v.dtype == o.dtype == k_cache.dtype == v_cache.dtype == q.dtype):
+                rot_mode: int = _lib.ROT_LAZY, is_mepic: bool = False, packed_block_table=None):
+    """Same checks and struct filling as the regular operators (one shared helper), for
+    16-bit caches; creates no tensor."""
+    if q.dtype not in _ACT or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
         raise ValueError("q, k, v, o and the caches must share one dtype out of float16/bfloat16")
-    a = _lib.LaPrefillArgs()
-    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
-    a.q_stride_t, a.q_stride_h = q.stride(0), q.stride(1)
-    a.k_stride_t, a.k_stride_h = k.stride(0), k.stride(1)
-    a.v_stride_t, a.v_stride_h = v.stride(0), v.stride(1)
-    a.o_stride_t, a.o_stride_h = o.stride(0), o.stride(1)
-    a.k_cache, a.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
-    a.kc_stride_block, a.kc_stride_head = k_cache.stride(0), k_cache.stride(1)
-    a.vc_stride_block, a.vc_stride_head = v_cache.stride(0), v_cache.stride(1)
-    a.num_blocks = k_cache.shape[0]
-    a.block_table = b_loc.data_ptr()
-    a.q_offset = None if q_offset is None else q_offset.data_ptr()
-    a.q_mask = None if q_mask is None else q_mask.data_ptr()
-    a.table_stride = b_loc.stride(0)
-    a.query_start_loc, a.seq_lens = b_start_loc.data_ptr(), b_seq_len.data_ptr()
-    if is_lazy is not None:
-        a.is_lazy = is_lazy.data_ptr()  # torch.bool is one byte per element
-    if cos_sin_cache is not None:
-        a.cos_sin_cache = cos_sin_cache.data_ptr()
-        a.cos_sin_rows = cos_sin_cache.shape[0]
-        a.cos_sin_dtype = _ACT[cos_sin_cache.dtype]
-    a.batch = b_seq_len.shape[0]
-    a.num_q_heads, a.num_kv_heads, a.head_dim = q.shape[1], k.shape[1], q.shape[2]
-    a.block_size, a.x = v_cache.shape[3], k_cache.shape[4]
-    a.max_query_len = int(max_input_len)
-    a.max_seq_len = int(max_seq_len)
-    a.q_dtype = a.kv_dtype = _ACT[q.dtype]
-    a.rotary_dim = q.shape[2]
-    a.skip_decode = int(bool(skip_decode))
-    a.rot_mode, a.is_mepic = int(rot_mode), int(bool(is_mepic))
-    a.sm_scale = float(sm_scale) if sm_scale is not None else 1.0 / (q.shape[2] ** 0.5)
-    return a
+    from .attention import prefill_args
+    return prefill_args(q, k, v, o, "auto", k_cache, v_cache, b_loc, b_start_loc, b_seq_len,
+                        max_seq_len, max_input_len, None, None, None, None, sm_scale, skip_decode,
+                        cos_sin_cache, None, True, is_lazy, q_offset, q_mask, int(rot_mode),
+                        bool(is_mepic), "tensor", None, packed_block_table)

@@ -247,6 +247,90 @@ def test_decode_covers_sequences_longer_than_max_seq_len(variant, op, bound):
     util.assert_close(got, want, what=f"decode with max_seq_len={bound}", **FP8)
 
 
+@pytest.mark.parametrize("kernel", ["general", "tensor"])
+@pytest.mark.parametrize("variant", ["lazy", "mepic"])
+def test_prefill_reads_the_packed_table(kernel, variant):
+    """One 8-byte packed entry per page instead of three int32 gathers: the result must be
+    the same bit for bit, also when the three tables hold garbage the kernel must not read."""
+    import lazy_attention_b200 as la
+    pool = [100, 64, 33, 250, 16, 129]
+    reqs = [dict(docs=[2, 0, 1], qlen=37), dict(docs=[3, 1, 5], qlen=300), dict(docs=[0], qlen=16, lazy=False)]
+    case = synth.build_prefill(synth.GEOM_8B, torch.bfloat16, pool, reqs, seed=7, variant=variant, device="cuda")
+    packed = util.pack_host(case).to("cuda")
+    fn = la.context_attention_fwd if variant == "lazy" else la.context_attention_fwd_mepic
+
+    def run(q_offset, q_mask, packed_table):
+        out = util.new_out(case)
+        kw = dict(is_lazy=case["is_lazy"]) if variant == "lazy" else {}
+        fn(case["q"], case["k"], case["v"], out, "auto", case["k_cache"], case["v_cache"], case["block_table"],
+           case["query_start_loc"], case["seq_lens"], case["max_seq_len"], case["max_query_len"],
+           case["k_scale"], case["v_scale"], sm_scale=case["sm_scale"], cos_sin_cache=case["cos_sin_cache"],
+           q_offset=q_offset, q_mask=q_mask, kernel=kernel, packed_block_table=packed_table, **kw)
+        torch.cuda.synchronize()
+        return out
+
+    want = run(case["q_offset"], case["q_mask"], None)
+    junk = torch.full_like(case["q_offset"], 12345)
+    got = run(junk, junk, packed)
+    assert torch.equal(got, want)
+    op = "lazy_prefill" if variant == "lazy" else "mepic_prefill"
+    util.assert_close(got.float().cpu(), util.run_oracle(case, op), what="packed-table prefill", **HALF)
+
+
+def _new_token_slots(case):
+    """slot = page * 16 + in-page index of every new token, from the block table (what the
+    engine's slot_mapping holds); one of them is marked as padding (-1)."""
+    bt = case["block_table"].cpu()
+    qsl = case["query_start_loc"].cpu().tolist()
+    seq = case["seq_lens"].cpu().tolist()
+    BS = case["geom"].block_size
+    slots = []
+    for b in range(len(seq)):
+        qlen = qsl[b + 1] - qsl[b]
+        for n in range(qlen):
+            pos = seq[b] - qlen + n
+            slots.append(int(bt[b, pos // BS]) * BS + pos % BS)
+    return torch.tensor(slots, dtype=torch.int64)
+
+
+@pytest.mark.parametrize("kernel", ["general", "tensor"])
+@pytest.mark.parametrize("kv", ["auto", "fp8_e4m3"])
+@pytest.mark.parametrize("variant,op", [("lazy", "lazy_op"), ("mepic", "mepic_op")])
+def test_fused_cache_write_equals_separate_write(kernel, kv, variant, op):
+    """With ``slot_mapping`` the attention call stores the new K/V rows itself: caches and
+    output must equal, bit for bit, a separate write_to_paged_cache followed by the call."""
+    import lazy_attention_b200 as la
+    reqs = [dict(docs=[2, 0, 1], qlen=37), dict(docs=[3, 1, 5], qlen=300), dict(docs=[1, 2, 4], qlen=1),
+            dict(docs=[0], qlen=16, lazy=False), dict(docs=[4, 3], qlen=1), dict(docs=[], qlen=20)]
+    ks, vs = (0.11, 0.07) if "fp8" in kv else (1.0, 1.0)
+    case = synth.build_prefill(synth.GEOM_8B, torch.bfloat16, POOL, reqs, seed=9, variant=variant, device="cuda",
+                               kv_dtype=kv, k_scale=ks, v_scale=vs)
+    case["packed_block_table"] = util.pack_host(case).cuda()
+    slots = _new_token_slots(case).cuda()
+    fn = la.chunked_prefill_paged_decode if variant == "lazy" else la.chunked_prefill_paged_decode_mepic
+
+    def run(kc, vc, slot_mapping):
+        out = util.new_out(case)
+        kw = dict(is_lazy=case["is_lazy"], packed_block_table=case["packed_block_table"]) if variant == "lazy" else {}
+        fn(case["q"], case["k"], case["v"], out, kv, kc, vc, case["block_table"], case["query_start_loc"],
+           case["seq_lens"], case["max_seq_len"], case["max_query_len"], case["k_scale"], case["v_scale"],
+           sm_scale=case["sm_scale"], cos_sin_cache=case["cos_sin_cache"], q_offset=case["q_offset"],
+           q_mask=case["q_mask"], kernel=kernel, slot_mapping=slot_mapping, **kw)
+        torch.cuda.synchronize()
+        assert la.device_status() == 0
+        return out
+
+    kc_a, vc_a = case["k_cache"].clone(), case["v_cache"].clone()
+    la.write_to_paged_cache(case["k"], case["v"], kc_a, vc_a, slots, kv, case["k_scale"], case["v_scale"])
+    out_a = run(kc_a, vc_a, None)
+    kc_b, vc_b = case["k_cache"].clone(), case["v_cache"].clone()
+    out_b = run(kc_b, vc_b, slots)
+    assert torch.equal(kc_a, kc_b), "K cache differs from the separate write"
+    assert torch.equal(vc_a, vc_b), "V cache differs from the separate write"
+    assert torch.equal(out_a, out_b), "attention output differs"
+    assert not torch.equal(kc_b, case["k_cache"]), "nothing was written"
+
+
 def test_empty_batch_and_skip_decode_leave_output_untouched():
     import lazy_attention_b200 as la
     case = util.to_device(util.load_golden("lazy_prefill_small"), "cuda")

@@ -738,6 +738,10 @@ def run_workload(name, args, world, rank, local_rank, device):
             tb["unit"] = "tokens/s"
             res["speedup_vs_triton"] = tb["ms_per_step"] / eager_ms
         res["triton_baseline"] = tb
+    if peers is not None:
+        torch.cuda.synchronize(device)
+        for pset in peers:
+            pset.close()
     return res
 
 

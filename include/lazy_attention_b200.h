@@ -150,6 +150,13 @@ typedef struct LaPrefillArgs {
    * can be dropped.  The caches are written through k_cache / v_cache although the struct
    * declares them const.  Requests the call skips (skip_decode) are not written. */
   const int64_t* slot_mapping;
+  /* Optional fused rotary op, int64 [num_tokens]: when non-NULL, q arrives WITHOUT rotary
+   * embedding and the kernel applies it (NeoX halves, row q_positions[t] of cos_sin_cache,
+   * result rounded to q's dtype) while it stages the query -- what the query-only rotary op
+   * does in place just before the attention op
+   * (lazy_attn/lazy/model_executor/layers/rotary_embedding.py:66-94).  q itself is not
+   * modified.  Tensor-core kernel only (LA_ERR_UNSUPPORTED otherwise). */
+  const int64_t* q_positions;
 } LaPrefillArgs;
 
 /*
@@ -212,6 +219,21 @@ typedef struct LaDecodeArgs {
   const void* value;
   int64_t k_stride_t, k_stride_h, v_stride_t, v_stride_h;
   const int64_t* slot_mapping;
+  /* Optional fused rotary op for the decode rows (see LaPrefillArgs.q_positions).
+   * Split-KV kernel only. */
+  const int64_t* q_positions;
+  /* Optional in-kernel cos/sin: with compute_cos_sin != 0 the rotation of the query by a
+   * page's offset takes cos/sin(position * inv_freq) computed in the kernel from these
+   * parameters instead of a row of cos_sin_cache (which may then be NULL unless q_positions
+   * is given) -- the reference's COMPUTE_COS_SIN path with the frequencies of
+   * lazy_attn/lazy/model_executor/rope/cos_sin.py:24-66; parameters as rope_meta_from_layer
+   * (:94-124) returns them.  rope_type: 0 = plain, 1 = llama3 smoothing.  Split-KV kernel,
+   * LA_ROT_LAZY only. */
+  int32_t compute_cos_sin;
+  int32_t rope_type;
+  float rope_base, rope_scaling_factor, rope_low_freq_factor, rope_high_freq_factor;
+  int32_t rope_orig_max_position;
+  int32_t reserved0;
 } LaDecodeArgs;
 
 /* Replaces context_attention_fwd / _fwd_kernel (see LaPrefillArgs). */
@@ -311,6 +333,23 @@ typedef struct LaWriteCacheArgs {
 } LaWriteCacheArgs;
 
 int la_write_paged_cache(const LaWriteCacheArgs* args, void* stream);
+
+/*
+ * Buffers for the fused output gather (LaPeerOut), shared between the processes of one node
+ * with CUDA IPC.  No counterpart in the reference (its ranks gather with a collective).
+ *   la_peer_alloc   cudaMalloc of `bytes` on the current device, zero-filled
+ *   la_peer_export  the 64-byte CUDA IPC handle of a buffer from la_peer_alloc
+ *   la_peer_open    maps another process's buffer into this process for the CURRENT device
+ *                   (the device whose kernels will store through the mapping)
+ *   la_peer_close   unmaps a pointer from la_peer_open
+ *   la_peer_free    frees a buffer from la_peer_alloc (after every peer has closed it)
+ */
+#define LA_IPC_HANDLE_BYTES 64
+int la_peer_alloc(size_t bytes, void** out);
+int la_peer_export(const void* buffer, unsigned char handle[LA_IPC_HANDLE_BYTES]);
+int la_peer_open(const unsigned char handle[LA_IPC_HANDLE_BYTES], void** out);
+int la_peer_close(void* mapped);
+int la_peer_free(void* buffer);
 
 /* Text of the last error on this thread ("" if none). */
 const char* la_last_error(void);

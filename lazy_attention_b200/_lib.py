@@ -25,6 +25,7 @@ EXPORTS = (
     "la_build_cos_sin_table", "la_last_error", "la_version", "la_launch_count",
     "la_sizeof_prefill_args", "la_sizeof_decode_args", "la_device_status",
     "la_prefill_fwd_noalloc", "la_write_paged_cache",
+    "la_peer_alloc", "la_peer_export", "la_peer_open", "la_peer_close", "la_peer_free",
 )
 
 
@@ -66,6 +67,7 @@ class LaPrefillArgs(C.Structure):
         ("peer", LaPeerOut),
         ("packed_block_table", C.c_void_p), ("packed_stride", C.c_int64),
         ("slot_mapping", C.c_void_p),
+        ("q_positions", C.c_void_p),
     ]
 
 
@@ -95,6 +97,11 @@ class LaDecodeArgs(C.Structure):
         ("k_stride_t", C.c_int64), ("k_stride_h", C.c_int64),
         ("v_stride_t", C.c_int64), ("v_stride_h", C.c_int64),
         ("slot_mapping", C.c_void_p),
+        ("q_positions", C.c_void_p),
+        ("compute_cos_sin", C.c_int32), ("rope_type", C.c_int32),
+        ("rope_base", C.c_float), ("rope_scaling_factor", C.c_float),
+        ("rope_low_freq_factor", C.c_float), ("rope_high_freq_factor", C.c_float),
+        ("rope_orig_max_position", C.c_int32), ("reserved0", C.c_int32),
     ]
 
 
@@ -152,6 +159,13 @@ def load() -> C.CDLL:
     lib.la_launch_count.restype = C.c_int64
     lib.la_device_status.argtypes = []
     lib.la_device_status.restype = C.c_int
+    lib.la_peer_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]
+    lib.la_peer_export.argtypes = [C.c_void_p, C.c_char_p]
+    lib.la_peer_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+    lib.la_peer_close.argtypes = [C.c_void_p]
+    lib.la_peer_free.argtypes = [C.c_void_p]
+    for fn in (lib.la_peer_alloc, lib.la_peer_export, lib.la_peer_open, lib.la_peer_close, lib.la_peer_free):
+        fn.restype = C.c_int
     lib.la_sizeof_prefill_args.restype = C.c_size_t
     lib.la_sizeof_decode_args.restype = C.c_size_t
     if (lib.la_sizeof_prefill_args() != C.sizeof(LaPrefillArgs)

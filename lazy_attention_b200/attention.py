@@ -150,6 +150,15 @@ def _slots(slot_mapping, num_rows):
     return slot_mapping.data_ptr()
 
 
+def _positions(positions):
+    """Pointer of the token positions of a fused rotary op (None: the query is already rotated)."""
+    if positions is None:
+        return None
+    if positions.dtype != torch.int64 or not positions.is_cuda or not positions.is_contiguous():
+        raise ValueError("positions must be a contiguous int64 CUDA tensor")
+    return positions.data_ptr()
+
+
 def _scale(t, device):
     if torch.is_tensor(t):
         if t.dtype != torch.float32 or not t.is_cuda:
@@ -162,7 +171,7 @@ def prefill_args(q, k, v, o, kv_cache_dtype, k_cache, v_cache, b_loc, b_start_lo
                  max_seq_len, max_input_len, k_scale, v_scale, alibi_slopes, sliding_window,
                  sm_scale, skip_decode, cos_sin_cache, rotary_dim, is_neox_style, is_lazy,
                  q_offset, q_mask, rot_mode, is_mepic, kernel, peer_out=None,
-                 packed_block_table=None, slot_mapping=None) -> LaPrefillArgs:
+                 packed_block_table=None, slot_mapping=None, positions=None) -> LaPrefillArgs:
     """Checks the tensors of a prefix-prefill call the way the reference wrapper does
     (ops/prefix_prefill.py:626-674: fp8 views, dtype and shape assertions, alibi refusal)
     plus what a raw-pointer interface must know (devices, dtypes of the int tables, unit
@@ -219,6 +228,7 @@ def prefill_args(q, k, v, o, kv_cache_dtype, k_cache, v_cache, b_loc, b_start_lo
         a.packed_block_table = packed_block_table.data_ptr()
         a.packed_stride = packed_block_table.stride(0)
     a.slot_mapping = _slots(slot_mapping, q.shape[0])
+    a.q_positions = _positions(positions)
     a.query_start_loc, a.seq_lens = b_start_loc.data_ptr(), b_seq_len.data_ptr()
     a.is_lazy = _ptr(_bool_u8(is_lazy))  # a view of the caller's tensor: same storage
     if kv_code in (_lib.DTYPE_FP8_E4M3, _lib.DTYPE_FP8_E5M2) or k_scale is not None:
@@ -268,7 +278,8 @@ def context_attention_fwd(q, k, v, o, kv_cache_dtype: str, k_cache, v_cache, b_l
                           v_scale: torch.Tensor, alibi_slopes=None, sliding_window=None,
                           sm_scale=None, skip_decode=False, cos_sin_cache=None, rotary_dim=None,
                           is_neox_style=True, is_lazy=None, q_offset=None, q_mask=None,
-                          kernel=None, peer_out=None, packed_block_table=None, slot_mapping=None):
+                          kernel=None, peer_out=None, packed_block_table=None, slot_mapping=None,
+                          positions=None):
     """Prefix-prefill attention, per-page rotation variant.  Writes ``o`` in place.
 
     For a lazy request every cached page's K is rotated forward by
@@ -281,12 +292,16 @@ def context_attention_fwd(q, k, v, o, kv_cache_dtype: str, k_cache, v_cache, b_l
     count as one 8-byte entry instead of three gathers.  ``slot_mapping`` (also an
     addition) makes the call store the new K/V rows into the caches itself: the
     ``write_to_paged_cache`` that precedes the op in the reference backend
-    (backends/triton_attn.py:100-109) is then not needed.
+    (backends/triton_attn.py:100-109) is then not needed.  ``positions`` (int64 per
+    token, an addition too) fuses the query-only rotary op that runs just before the
+    attention op (model_executor/layers/rotary_embedding.py:66-94): ``q`` is then
+    passed without rotary embedding and is rotated as the kernel stages it.
     """
     _prefill(q, k, v, o, kv_cache_dtype, k_cache, v_cache, b_loc, b_start_loc, b_seq_len,
              max_seq_len, max_input_len, k_scale, v_scale, alibi_slopes, sliding_window,
              sm_scale, skip_decode, cos_sin_cache, rotary_dim, is_neox_style, is_lazy,
-             q_offset, q_mask, _lib.ROT_LAZY, False, kernel, peer_out, packed_block_table, slot_mapping)
+             q_offset, q_mask, _lib.ROT_LAZY, False, kernel, peer_out, packed_block_table, slot_mapping,
+             positions)
 
 
 @torch.inference_mode()
@@ -297,20 +312,22 @@ def context_attention_fwd_mepic(q, k, v, o, kv_cache_dtype: str, k_cache, v_cach
                                 cos_sin_cache=None, rotary_dim=None, is_neox_style=True,
                                 q_mask=None, q_offset=None, is_mepic: bool = True,
                                 force_fp32_rotary: bool = False, kernel=None, peer_out=None,
-                                packed_block_table=None, slot_mapping=None):
+                                packed_block_table=None, slot_mapping=None, positions=None):
     """Prefix-prefill attention, per-token rotation variant: cached K is rotated
     at each token's slot position, new K at ``ctx_len + n``.  The rotation is
     always evaluated in float32 (``force_fp32_rotary`` is accepted and implied)."""
     _prefill(q, k, v, o, kv_cache_dtype, k_cache, v_cache, b_loc, b_start_loc, b_seq_len,
              max_seq_len, max_input_len, k_scale, v_scale, alibi_slopes, sliding_window,
              sm_scale, skip_decode, cos_sin_cache, rotary_dim, is_neox_style, None,
-             q_offset, q_mask, _lib.ROT_MEPIC, is_mepic, kernel, peer_out, packed_block_table, slot_mapping)
+             q_offset, q_mask, _lib.ROT_MEPIC, is_mepic, kernel, peer_out, packed_block_table, slot_mapping,
+             positions)
 
 
 def _decode(query, output, kv_cache_dtype, key_cache, value_cache, query_start_loc, seq_lens,
             max_seq_len, k_scale, v_scale, alibi_slopes, sliding_window, sm_scale, rotary_dim,
             cos_sin_cache, is_lazy, packed_block_table, block_table, q_mask, rot_mode,
-            ignore_q_mask, kernel, peer_out=None, key=None, value=None, slot_mapping=None):
+            ignore_q_mask, kernel, peer_out=None, key=None, value=None, slot_mapping=None, positions=None,
+            rope_meta=None):
     kv_code = _fp8_view(kv_cache_dtype, key_cache, value_cache)
     _require_cuda(query, output, key_cache, value_cache, query_start_loc, seq_lens)
     if query.dtype not in _ACT or output.dtype != query.dtype:
@@ -377,6 +394,16 @@ def _decode(query, output, kv_cache_dtype, key_cache, value_cache, query_start_l
         a.k_stride_t, a.k_stride_h = key.stride(0), key.stride(1)
         a.v_stride_t, a.v_stride_h = value.stride(0), value.stride(1)
         a.slot_mapping = _slots(slot_mapping, query.shape[0])
+    a.q_positions = _positions(positions)
+    if rope_meta is not None:
+        # in-kernel cos/sin from the rotary layer's parameters (keys of rope_meta_from_layer)
+        a.compute_cos_sin = 1
+        a.rope_type = int(rope_meta.get("ROPE_TYPE", 0))
+        a.rope_base = float(rope_meta.get("BASE", 10000.0))
+        a.rope_scaling_factor = float(rope_meta.get("SCALING_FACTOR", 1.0))
+        a.rope_low_freq_factor = float(rope_meta.get("LOW_FACTOR", 1.0))
+        a.rope_high_freq_factor = float(rope_meta.get("HIGH_FACTOR", 1.0))
+        a.rope_orig_max_position = int(rope_meta.get("ORIG_MAX_POSITION", 8192))
     lib = _lib.load()
     need = lib.la_decode_workspace_bytes(C.byref(a))
     ws = _workspace(query.device, need)
@@ -387,6 +414,17 @@ def _decode(query, output, kv_cache_dtype, key_cache, value_cache, query_start_l
     _lib.check(rc, "la_decode_fwd")
 
 
+def _decode_rope_meta(rope_meta):
+    """RoPE parameters for in-kernel cos/sin, or None to load them from the table
+    (the reference's switch, lazy_attn/lazy/utils/variants.py:136-137)."""
+    if not _env_flag("LAZY_DECODE_COMPUTE_COS_SIN"):
+        return None
+    if rope_meta is not None:
+        return rope_meta
+    return dict(ROPE_TYPE=0, BASE=10000.0, SCALING_FACTOR=1.0, LOW_FACTOR=1.0, HIGH_FACTOR=1.0,
+                ORIG_MAX_POSITION=8192)
+
+
 @torch.inference_mode()
 def chunked_prefill_paged_decode(query, key, value, output, kv_cache_dtype, key_cache, value_cache,
                                  block_table, query_start_loc, seq_lens, max_seq_len,
@@ -394,14 +432,19 @@ def chunked_prefill_paged_decode(query, key, value, output, kv_cache_dtype, key_
                                  sliding_window=None, sm_scale=None, rotary_dim=None, freqs=None,
                                  cos_sin_cache=None, rope_meta=None, is_neox_style=True,
                                  is_lazy=None, lazy_variant=None, q_offset=None, q_mask=None,
-                                 packed_block_table=None, kernel=None, peer_out=None, slot_mapping=None):
+                                 packed_block_table=None, kernel=None, peer_out=None, slot_mapping=None,
+                                 positions=None):
     """One attention-layer call on a mixed batch: prefix-prefill for requests with
     more than one query token, paged decode for those with exactly one.
 
     Keeps the reference's quirks: the default ``sm_scale`` is
     ``1/sqrt(query.shape[1])`` (the head count), ``NO_LAZY=1`` clears
     ``is_lazy`` in place, and the decode kernel reads block ids from the packed
-    table's high half, so ``packed_block_table`` is required for decode.
+    table's high half, so ``packed_block_table`` is required for decode.  As in the
+    reference (ops/chunked_prefill_paged_decode.py:146-155) the decode kernel loads
+    cos/sin from ``cos_sin_cache`` unless ``LAZY_DECODE_COMPUTE_COS_SIN=1``, in which
+    case it computes them from ``rope_meta`` (plain RoPE with base 10000 when that is
+    missing, the reference's default); ``freqs`` is accepted and unused, as there.
     """
     if _env_flag("NO_LAZY") and is_lazy is not None:
         is_lazy.fill_(False)
@@ -419,7 +462,8 @@ def chunked_prefill_paged_decode(query, key, value, output, kv_cache_dtype, key_
                               rotary_dim=rotary_dim, cos_sin_cache=cos_sin_cache,
                               is_neox_style=is_neox_style, is_lazy=is_lazy, q_offset=q_offset,
                               q_mask=q_mask, kernel=kernel, peer_out=peer_out,
-                              packed_block_table=packed_block_table, slot_mapping=slot_mapping)
+                              packed_block_table=packed_block_table, slot_mapping=slot_mapping,
+                              positions=positions)
     table = packed_block_table
     if table is None:
         # The reference would hand the kernel the plain table and unpack garbage
@@ -428,7 +472,8 @@ def chunked_prefill_paged_decode(query, key, value, output, kv_cache_dtype, key_
     _decode(query, output, kv_cache_dtype, key_cache, value_cache, query_start_loc, seq_lens,
             max_seq_len, k_scale, v_scale, alibi_slopes, sliding_window, sm_scale, rotary_dim,
             cos_sin_cache, is_lazy, table, None, None, _lib.ROT_LAZY,
-            _env_flag("LAZY_DECODE_IGNORE_Q_MASK"), kernel, peer_out, key, value, slot_mapping)
+            _env_flag("LAZY_DECODE_IGNORE_Q_MASK"), kernel, peer_out, key, value, slot_mapping, positions,
+            _decode_rope_meta(rope_meta))
 
 
 @torch.inference_mode()
@@ -439,7 +484,7 @@ def chunked_prefill_paged_decode_mepic(query, key, value, output, kv_cache_dtype
                                        rotary_dim=None, cos_sin_cache=None, is_neox_style=True,
                                        q_offset=None, q_mask=None, is_mepic: bool = True,
                                        force_fp32_rotary: bool = False, kernel=None, peer_out=None,
-                                       slot_mapping=None):
+                                       slot_mapping=None, positions=None):
     """Per-token rotation twin of :func:`chunked_prefill_paged_decode`: plain
     int32 block table and ``q_mask``; missing ``q_mask`` / ``q_offset`` mean zeros."""
     if sm_scale is None:
@@ -462,8 +507,8 @@ def chunked_prefill_paged_decode_mepic(query, key, value, output, kv_cache_dtype
                                     cos_sin_cache=cos_sin_cache, is_neox_style=is_neox_style,
                                     q_mask=q_mask, q_offset=q_offset, is_mepic=is_mepic,
                                     force_fp32_rotary=force_fp32_rotary, kernel=kernel,
-                                    peer_out=peer_out, slot_mapping=slot_mapping)
+                                    peer_out=peer_out, slot_mapping=slot_mapping, positions=positions)
     _decode(query, output, kv_cache_dtype, key_cache, value_cache, query_start_loc, seq_lens,
             max_seq_len, k_scale, v_scale, alibi_slopes, sliding_window, sm_scale, rotary_dim,
             cos_sin_cache, None, None, block_table, q_mask, _lib.ROT_MEPIC, False, kernel, peer_out,
-            key, value, slot_mapping)
+            key, value, slot_mapping, positions)

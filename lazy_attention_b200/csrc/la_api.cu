@@ -94,8 +94,8 @@ int validate_decode(const LaDecodeArgs* a) {
     LA_REQUIRE(a->packed_block_table != nullptr, LA_ERR_INVALID_ARGUMENT,
                "la_decode_fwd: lazy mode needs the packed block table");
     if (a->is_lazy)
-      LA_REQUIRE(a->cos_sin_cache != nullptr && a->cos_sin_rows > 0, LA_ERR_INVALID_ARGUMENT,
-                 "la_decode_fwd: rotation requested without a cos/sin table");
+      LA_REQUIRE((a->cos_sin_cache != nullptr && a->cos_sin_rows > 0) || a->compute_cos_sin, LA_ERR_INVALID_ARGUMENT,
+                 "la_decode_fwd: rotation requested without a cos/sin table or RoPE parameters");
   } else if (a->rot_mode == LA_ROT_MEPIC) {
     LA_REQUIRE(a->block_table != nullptr && a->q_mask != nullptr, LA_ERR_INVALID_ARGUMENT,
                "la_decode_fwd: per-token mode needs block_table and q_mask");
@@ -140,9 +140,12 @@ extern "C" int la_prefill_fwd(const LaPrefillArgs* args, void* stream) {
   };
   if (args->kernel == LA_KERNEL_GENERAL) {
     LA_REQUIRE(args->peer.num_peers == 0, LA_ERR_UNSUPPORTED, "la_prefill_fwd: the general kernel has no fused output gather");
+    LA_REQUIRE(args->q_positions == nullptr, LA_ERR_UNSUPPORTED, "la_prefill_fwd: the general kernel has no fused rotary op");
     return general();
   }
   const bool tc_ok = tc_prefill_supported(*args, &why);
+  LA_REQUIRE(tc_ok || args->q_positions == nullptr, LA_ERR_UNSUPPORTED,
+             "la_prefill_fwd: the fused rotary op needs the tensor-core kernel, unavailable here: %s", why);
   if (args->kernel == LA_KERNEL_TENSOR) {
     LA_REQUIRE(tc_ok, LA_ERR_UNSUPPORTED, "la_prefill_fwd: tensor-core kernel unavailable: %s", why);
     return launch_tc_prefill(*args, s);
@@ -180,9 +183,14 @@ extern "C" int la_decode_fwd(const LaDecodeArgs* args, void* stream) {
   };
   if (args->kernel == LA_KERNEL_GENERAL) {
     LA_REQUIRE(args->peer.num_peers == 0, LA_ERR_UNSUPPORTED, "la_decode_fwd: the general kernel has no fused output gather");
+    LA_REQUIRE(args->q_positions == nullptr && !(args->compute_cos_sin && args->cos_sin_cache == nullptr),
+               LA_ERR_UNSUPPORTED, "la_decode_fwd: the general kernel has no fused rotary op / in-kernel cos/sin");
     return general();
   }
   const bool fast_ok = fast_decode_supported(*args, &why);
+  LA_REQUIRE(fast_ok || (args->q_positions == nullptr && !(args->compute_cos_sin && args->cos_sin_cache == nullptr)),
+             LA_ERR_UNSUPPORTED,
+             "la_decode_fwd: the fused rotary op / in-kernel cos/sin need the split-KV kernel, unavailable here: %s", why);
   if (args->kernel == LA_KERNEL_TENSOR) {
     LA_REQUIRE(fast_ok, LA_ERR_UNSUPPORTED, "la_decode_fwd: split-KV kernel unavailable: %s", why);
     return launch_fast_decode(*args, s);
@@ -222,4 +230,52 @@ extern "C" int la_device_status(void) {
     LA_CHECK_CUDA(cudaMemcpyToSymbol(la::g_device_status, zero, sizeof(zero)));
   }
   return host[0];
+}
+
+// ---- buffers of the fused output gather, shared across processes with CUDA IPC ---------------
+extern "C" int la_peer_alloc(size_t bytes, void** out) {
+  LA_REQUIRE(out != nullptr && bytes > 0, LA_ERR_INVALID_ARGUMENT, "la_peer_alloc: null result or zero size");
+  *out = nullptr;
+  void* ptr = nullptr;
+  LA_CHECK_CUDA(cudaMalloc(&ptr, bytes));
+  cudaError_t e = cudaMemset(ptr, 0, bytes);
+  if (e != cudaSuccess) {
+    cudaFree(ptr);
+    la::set_error("la_peer_alloc: cudaMemset failed: %s", cudaGetErrorString(e));
+    return LA_ERR_CUDA;
+  }
+  *out = ptr;
+  return LA_OK;
+}
+
+extern "C" int la_peer_export(const void* buffer, unsigned char handle[LA_IPC_HANDLE_BYTES]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == LA_IPC_HANDLE_BYTES, "IPC handle size");
+  LA_REQUIRE(buffer != nullptr && handle != nullptr, LA_ERR_INVALID_ARGUMENT, "la_peer_export: null argument");
+  cudaIpcMemHandle_t h;
+  LA_CHECK_CUDA(cudaIpcGetMemHandle(&h, const_cast<void*>(buffer)));
+  std::memcpy(handle, &h, sizeof(h));
+  return LA_OK;
+}
+
+extern "C" int la_peer_open(const unsigned char handle[LA_IPC_HANDLE_BYTES], void** out) {
+  LA_REQUIRE(handle != nullptr && out != nullptr, LA_ERR_INVALID_ARGUMENT, "la_peer_open: null argument");
+  *out = nullptr;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, sizeof(h));
+  void* ptr = nullptr;
+  LA_CHECK_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  *out = ptr;
+  return LA_OK;
+}
+
+extern "C" int la_peer_close(void* mapped) {
+  if (mapped == nullptr) return LA_OK;
+  LA_CHECK_CUDA(cudaIpcCloseMemHandle(mapped));
+  return LA_OK;
+}
+
+extern "C" int la_peer_free(void* buffer) {
+  if (buffer == nullptr) return LA_OK;
+  LA_CHECK_CUDA(cudaFree(buffer));
+  return LA_OK;
 }

@@ -55,6 +55,10 @@ struct DecParams {
   const void* value;
   int64_t k_st, k_sh, v_st, v_sh;
   const int64_t* slots;
+  const int64_t* q_pos;  // fused rotary op on the query (nullptr: the query arrives rotated)
+  // in-kernel cos/sin (compute_cs != 0): parameters of the inverse frequencies
+  int compute_cs, rope_type, rope_orig;
+  float rope_base, rope_factor, rope_low, rope_high;
   float* part_o;   // [num_seqs][Hq][n_splits][D]
   float* part_ml;  // [num_seqs][Hq][n_splits][2]
   int* status;
@@ -163,6 +167,20 @@ __device__ __forceinline__ void to_cache_elems(const uint16_t* src, int n, uint8
   }
 }
 
+// Inverse RoPE frequency of dimension pair i of D/2, float32, with the llama3 wavelength
+// smoothing when rope_type == 1 (lazy_attn/lazy/model_executor/rope/cos_sin.py:38-59).
+template <int D>
+__device__ __forceinline__ float rope_inv_freq(const DecParams& p, int i) {
+  const float inv = 1.0f / powf(p.rope_base, (float)(2 * i) / (float)D);
+  if (p.rope_type != 1) return inv;
+  const float wave_len = 6.283185307179586f / inv;
+  const float low_wl = (float)p.rope_orig / p.rope_low, high_wl = (float)p.rope_orig / p.rope_high;
+  if (wave_len < high_wl) return inv;
+  if (wave_len > low_wl) return inv / p.rope_factor;
+  const float smooth = ((float)p.rope_orig / wave_len - p.rope_low) / (p.rope_high - p.rope_low);
+  return (1.f - smooth) * inv / p.rope_factor + smooth * inv;
+}
+
 // One output element: to `out`, or with the fused gather to the same place of every rank's buffer.
 template <bool BF16>
 __device__ __forceinline__ void store_result(const DecParams& p, int row_q, int head, int d, float val) {
@@ -185,7 +203,10 @@ __device__ __forceinline__ void store_result(const DecParams& p, int row_q, int 
     *reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(p.peer.out[q]) + off) = bits;
 }
 
-template <int D, int KV, bool BF16, bool MEPIC>
+// EXTRA: the optional fusions (cache write of the new token, rotary op on the query, cos/sin
+// computed in the kernel) are compiled into a second instance of the kernel, so that the
+// plain call keeps the register budget and instruction count its bandwidth depends on.
+template <int D, int KV, bool BF16, bool MEPIC, bool EXTRA>
 __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBlocks) decode_split_kernel(DecParams p) {
   using Cfg = DecCfg<D, KV>;
   constexpr bool BF16MMA = (KV == 0) && BF16;  // fp8 caches go through f16
@@ -229,6 +250,33 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
       qfull[ks][0] = v.x;
       qfull[ks][1] = v.y;
     }
+    if (EXTRA && p.q_pos != nullptr) {
+      // Fused rotary op: the query arrives without rotary embedding; rotate it forward at its
+      // position (NeoX halves: dims d and d + D/2 sit in k-steps ks and ks + KSTEPS/2 of this
+      // thread) and round to the query's dtype, as the stand-alone op leaves it.
+      int64_t pos = p.q_pos[row_q];
+      if (p.cs != nullptr && pos >= p.cs_rows) pos = p.cs_rows - 1;
+      const uint8_t* crow = reinterpret_cast<const uint8_t*>(p.cs) + pos * D * 2;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS / 2; ++ks) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          float2 cc, ss;
+          if (p.cs != nullptr) {
+            cc = unpack_q<BF16>(*reinterpret_cast<const uint32_t*>(crow + (ks * 16 + c * 4 + 2 * j) * 2));
+            ss = unpack_q<BF16>(*reinterpret_cast<const uint32_t*>(crow + D + (ks * 16 + c * 4 + 2 * j) * 2));
+          } else {
+            const float t0 = (float)pos * rope_inv_freq<D>(p, ks * 16 + c * 4 + 2 * j);
+            const float t1 = (float)pos * rope_inv_freq<D>(p, ks * 16 + c * 4 + 2 * j + 1);
+            cc = make_float2(cosf(t0), cosf(t1));
+            ss = make_float2(sinf(t0), sinf(t1));
+          }
+          const float2 q1 = unpack_q<BF16>(qfull[ks][j]), q2 = unpack_q<BF16>(qfull[ks + KSTEPS / 2][j]);
+          qfull[ks][j] = pack_mma<BF16>(q1.x * cc.x - q2.x * ss.x, q1.y * cc.y - q2.y * ss.y);
+          qfull[ks + KSTEPS / 2][j] = pack_mma<BF16>(q2.x * cc.x + q1.x * ss.x, q2.y * cc.y + q1.y * ss.y);
+        }
+      }
+    }
   }
   auto set_rotation = [&](int eff) {
     if (eff <= 1) {
@@ -241,18 +289,33 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
       return;
     }
     int pos = eff - 1;
-    if (pos >= p.cs_rows) pos = (int)p.cs_rows - 1;
+    if (!(EXTRA && p.compute_cs) && pos >= p.cs_rows) pos = (int)p.cs_rows - 1;
     const uint8_t* crow = reinterpret_cast<const uint8_t*>(p.cs) + (int64_t)pos * D * 2;
 #pragma unroll
     for (int ks = 0; ks < KSTEPS / 2; ++ks) {
       // dims d = 16ks + 4c + {0..3} pair with d + D/2, which sit in k-step ks + KSTEPS/2
-      const uint2 cv = __ldg(reinterpret_cast<const uint2*>(crow + (ks * 16 + c * 4) * 2));
-      const uint2 sv = __ldg(reinterpret_cast<const uint2*>(crow + D + (ks * 16 + c * 4) * 2));
-      const uint32_t cw[2] = {cv.x, cv.y}, sw[2] = {sv.x, sv.y};
+      const bool compute_cs = EXTRA && p.compute_cs != 0;
+      uint32_t cw[2] = {0, 0}, sw[2] = {0, 0};
+      if (!compute_cs) {
+        const uint2 cv = __ldg(reinterpret_cast<const uint2*>(crow + (ks * 16 + c * 4) * 2));
+        const uint2 sv = __ldg(reinterpret_cast<const uint2*>(crow + D + (ks * 16 + c * 4) * 2));
+        cw[0] = cv.x; cw[1] = cv.y; sw[0] = sv.x; sw[1] = sv.y;
+      }
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const float2 q1 = unpack_q<BF16>(qfull[ks][j]), q2 = unpack_q<BF16>(qfull[ks + KSTEPS / 2][j]);
-        const float2 cc = unpack_q<BF16>(cw[j]), ss = unpack_q<BF16>(sw[j]);
+        float2 cc, ss;
+        if (compute_cs) {
+          // cos/sin(position * inv_freq) in float32, not rounded to the table's dtype (the
+          // reference's COMPUTE_COS_SIN branch, ops/models/llama_v1.py:212-214)
+          const float t0 = (float)(eff - 1) * rope_inv_freq<D>(p, ks * 16 + c * 4 + 2 * j);
+          const float t1 = (float)(eff - 1) * rope_inv_freq<D>(p, ks * 16 + c * 4 + 2 * j + 1);
+          cc = make_float2(cosf(t0), cosf(t1));
+          ss = make_float2(sinf(t0), sinf(t1));
+        } else {
+          cc = unpack_q<BF16>(cw[j]);
+          ss = unpack_q<BF16>(sw[j]);
+        }
         // inverse rotation; rounded to the query's storage type as the reference does
         float n1x = q1.x * cc.x + q2.x * ss.x, n1y = q1.y * cc.y + q2.y * ss.y;
         float n2x = q2.x * cc.x - q1.x * ss.x, n2y = q2.y * cc.y - q1.y * ss.y;
@@ -366,7 +429,7 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
     if (!ok) break;
     const int pg = PPT * tl;
     const int np = min(PPT, n - pg);
-    if (p.slots != nullptr) {
+    if (EXTRA && p.slots != nullptr) {
       // Fused cache write: the warp whose tile holds the sequence's last page puts the new
       // token's K/V row (in cache format) into the landed copy of the page, so that this call
       // attends to it, and into the page in global memory for the calls to come.
@@ -683,10 +746,10 @@ int quantum_for(const LaDecodeArgs& a) {
   return 4 * (page_bytes > 2048 ? 1 : 2);
 }
 
-template <int D, int KV, bool BF16, bool MEPIC>
+template <int D, int KV, bool BF16, bool MEPIC, bool EXTRA>
 int launch_dec_m(const LaDecodeArgs& a, DecParams& p, cudaStream_t stream) {
   using Cfg = DecCfg<D, KV>;
-  auto kern = decode_split_kernel<D, KV, BF16, MEPIC>;
+  auto kern = decode_split_kernel<D, KV, BF16, MEPIC, EXTRA>;
   // the attribute is per device: remember on which devices this kernel has been prepared
   static std::atomic<uint64_t> prepared{0};
   int dev = 0;
@@ -710,8 +773,10 @@ int launch_dec_m(const LaDecodeArgs& a, DecParams& p, cudaStream_t stream) {
 
 template <int D, int KV, bool BF16>
 int launch_dec(const LaDecodeArgs& a, DecParams& p, cudaStream_t stream) {
-  return a.rot_mode == LA_ROT_MEPIC ? launch_dec_m<D, KV, BF16, true>(a, p, stream)
-                                    : launch_dec_m<D, KV, BF16, false>(a, p, stream);
+  const bool extra = a.slot_mapping != nullptr || a.q_positions != nullptr || a.compute_cos_sin != 0;
+  if (a.rot_mode == LA_ROT_MEPIC)
+    return extra ? launch_dec_m<D, KV, BF16, true, true>(a, p, stream) : launch_dec_m<D, KV, BF16, true, false>(a, p, stream);
+  return extra ? launch_dec_m<D, KV, BF16, false, true>(a, p, stream) : launch_dec_m<D, KV, BF16, false, false>(a, p, stream);
 }
 
 }  // namespace
@@ -727,6 +792,10 @@ bool fast_decode_supported(const LaDecodeArgs& a, const char** why) {
   if (a.alibi_slopes != nullptr) { *why = "alibi"; return false; }
   if (a.sliding_window > 0) { *why = "sliding window"; return false; }
   if (a.is_lazy != nullptr && a.cos_sin_cache != nullptr && a.cos_sin_dtype != a.q_dtype) { *why = "cos/sin table dtype must equal the query dtype"; return false; }
+  if (a.compute_cos_sin && a.rot_mode != LA_ROT_LAZY) { *why = "in-kernel cos/sin is for the per-page rotation mode"; return false; }
+  if (a.compute_cos_sin && (a.rope_base <= 1.f || (a.rope_type == 1 && (a.rope_high_freq_factor == a.rope_low_freq_factor || a.rope_scaling_factor <= 0.f)))) { *why = "bad RoPE parameters"; return false; }
+  if (a.q_positions != nullptr && a.cos_sin_cache == nullptr && !a.compute_cos_sin) { *why = "the fused rotary op needs the cos/sin table or the RoPE parameters"; return false; }
+  if (a.q_positions != nullptr && a.cos_sin_cache != nullptr && a.cos_sin_dtype != a.q_dtype) { *why = "cos/sin table dtype must equal the query dtype"; return false; }
   if (a.q_stride_t % 4 || a.q_stride_h % 4) { *why = "query strides must be multiples of 4 elements"; return false; }
   const int e = a.kv_dtype == a.q_dtype ? 2 : 1;
   if ((a.kc_stride_block * e) % 16 || (a.kc_stride_head * e) % 16 || (a.vc_stride_block * e) % 16 || (a.vc_stride_head * e) % 16) { *why = "cache strides must be multiples of 16 bytes"; return false; }
@@ -761,6 +830,10 @@ int launch_fast_decode(const LaDecodeArgs& a, cudaStream_t stream) {
   p.k_scale = a.k_scale; p.v_scale = a.v_scale;
   p.peer = a.peer;
   p.key = a.key; p.value = a.value; p.slots = a.slot_mapping;
+  p.q_pos = a.q_positions;
+  p.compute_cs = a.compute_cos_sin; p.rope_type = a.rope_type; p.rope_orig = a.rope_orig_max_position;
+  p.rope_base = a.rope_base; p.rope_factor = a.rope_scaling_factor;
+  p.rope_low = a.rope_low_freq_factor; p.rope_high = a.rope_high_freq_factor;
   p.k_st = a.k_stride_t; p.k_sh = a.k_stride_h; p.v_st = a.v_stride_t; p.v_sh = a.v_stride_h;
   p.cs = a.cos_sin_cache; p.cs_rows = a.cos_sin_rows;
   p.Hq = a.num_q_heads; p.Hkv = a.num_kv_heads; p.G = a.num_q_heads / a.num_kv_heads;

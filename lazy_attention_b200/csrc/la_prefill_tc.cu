@@ -89,6 +89,7 @@ struct TcParams {
   const float* v_scale;
   // fused cache write: slots of the new tokens (nullptr = off), the caches as writable bytes
   const int64_t* slots;
+  const int64_t* q_pos;  // fused rotary op on the query (nullptr: the query arrives rotated)
   uint8_t* kcw;
   uint8_t* vcw;
   int64_t kcw_sb, kcw_sh, vcw_sb, vcw_sh;  // bytes
@@ -503,7 +504,43 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
     // ---- Q tiles: rows R = row0 .. row0+255, chunk-coalesced global reads.  The softmax
     // warps have nothing to do until the first scores exist, so they stage Q while the
     // staging warps already work on the first K tile.
-    {
+    if (p.q_pos != nullptr) {
+      // Fused rotary op: q arrives without rotary embedding; each (chunk, chunk + D/2) pair of
+      // a row is rotated forward at the token's position while it is staged (same packed
+      // 16-bit arithmetic as the K rotation), q itself stays as it is.
+      const uint8_t* qb = reinterpret_cast<const uint8_t*>(p.q);
+      const uint8_t* csb = reinterpret_cast<const uint8_t*>(p.cs);
+#pragma unroll 2
+      for (int idx = tid; idx < kRowsPerCta * (NCH / 2); idx += kSoftmaxThreads) {
+        const int row = idx / (NCH / 2), g = idx - row * (NCH / 2);
+        const int Rq = row0 + row;
+        const int tqq = Rq >> p.g_shift;
+        uint4 a = make_uint4(0, 0, 0, 0), bq = make_uint4(0, 0, 0, 0);
+        if (tqq < qlen) {
+          const int head = kvh * G + (Rq & (G - 1));
+          const uint8_t* qrow = qb + ((int64_t)(s0 + tqq) * p.q_st + (int64_t)head * p.q_sh) * 2;
+          a = *reinterpret_cast<const uint4*>(qrow + g * 16);
+          bq = *reinterpret_cast<const uint4*>(qrow + (g + NCH / 2) * 16);
+          int64_t pos = p.q_pos[s0 + tqq];
+          if (pos >= p.cs_rows) pos = p.cs_rows - 1;
+          if (pos > 0) {
+            const uint8_t* crow = csb + pos * D * 2;
+            const uint4 cv = __ldg(reinterpret_cast<const uint4*>(crow + g * 16));
+            const uint4 sv = __ldg(reinterpret_cast<const uint4*>(crow + D + g * 16));
+            rotate_chunk<BF16>(a, bq, cv, sv);
+          }
+          if constexpr (BF16 && !MB) {
+            a = bf16x8_to_f16x8(a);
+            bq = bf16x8_to_f16x8(bq);
+          }
+        }
+        uint8_t* dst = sQ + (row >> 3) * Cfg::kRowGroupBytes + (row & 7) * 16;
+        *reinterpret_cast<uint4*>(dst + g * 128) = a;
+        *reinterpret_cast<uint4*>(dst + (g + NCH / 2) * 128) = bq;
+      }
+      fence_proxy_async_smem();
+      arrive_at_leader(&bar_q_ready);
+    } else {
       const uint8_t* qb = reinterpret_cast<const uint8_t*>(p.q);
 #pragma unroll 4
       for (int idx = tid; idx < kRowsPerCta * NCH; idx += kSoftmaxThreads) {
@@ -1553,6 +1590,7 @@ bool tc_prefill_supported(const LaPrefillArgs& a, const char** why) {
        reinterpret_cast<uintptr_t>(a.out) | reinterpret_cast<uintptr_t>(a.k_cache) |
        reinterpret_cast<uintptr_t>(a.v_cache) | reinterpret_cast<uintptr_t>(a.cos_sin_cache)) & 15) { *why = "pointers must be 16-byte aligned"; return false; }
   if (a.num_blocks <= 0) { *why = "num_blocks not given"; return false; }
+  if (a.q_positions != nullptr && a.cos_sin_cache == nullptr) { *why = "the fused rotary op needs the cos/sin table"; return false; }
   if (a.peer.num_peers < 0 || a.peer.num_peers > LA_MAX_PEERS) { *why = "peer count out of range"; return false; }
   for (int q = 0; q < a.peer.num_peers; ++q)
     if (a.peer.out[q] == nullptr || (reinterpret_cast<uintptr_t>(a.peer.out[q]) & 15)) { *why = "peer output pointers must be non-null and 16-byte aligned"; return false; }
@@ -1661,6 +1699,7 @@ int launch_tc_with_scratch(const LaPrefillArgs& a, cudaStream_t stream, void* sc
   p.table_stride = a.table_stride;
   p.packed = a.packed_block_table; p.packed_stride = a.packed_stride;
   p.slots = a.slot_mapping;
+  p.q_pos = a.q_positions;
   {
     const int64_t e = a.kv_dtype == a.q_dtype ? 2 : 1;  // bytes per cache element
     p.kcw = reinterpret_cast<uint8_t*>(const_cast<void*>(a.k_cache));

@@ -117,12 +117,29 @@ def gather_request_outputs(local_out: torch.Tensor, rows_per_rank: Sequence[Sequ
     return full
 
 
+class _DeviceView:
+    """Exposes raw device memory to torch through the CUDA array interface (16-bit words)."""
+
+    def __init__(self, ptr: int, words: int):
+        self.__cuda_array_interface__ = dict(shape=(words,), typestr="<i2", data=(int(ptr), False), version=3)
+
+
+def _as_tensor(ptr: int, shape, dtype, device) -> torch.Tensor:
+    n = 1
+    for d in shape:
+        n *= int(d)
+    if torch.empty((), dtype=dtype).element_size() != 2:
+        raise ValueError("peer output buffers hold 16-bit elements (bf16 / fp16)")
+    return torch.as_tensor(_DeviceView(ptr, n), device=device).view(dtype).view(*shape)
+
+
 class PeerOutput:
     """Full-size output buffers of all ranks of one node, each mapped into every
     rank's process, for the gather fused into the kernels' epilogue.
 
-    Every rank allocates ``[rows, heads, head_dim]``, exports it with CUDA IPC and
-    opens the others'; the attention kernels then store each result row straight
+    Every rank allocates ``[rows, heads, head_dim]`` through the library
+    (``la_peer_alloc``), exports it with CUDA IPC (``la_peer_export``) and opens the
+    others' (``la_peer_open``); the attention kernels then store each result row straight
     into all of these buffers (``peer_out=`` of the operators), and
     :meth:`barrier` -- a one-element all-reduce on the current stream -- is all
     that remains of the collective.  ``head_offset`` is the position of this
@@ -131,50 +148,66 @@ class PeerOutput:
 
     The buffers are rewritten by the peers' next call: read :attr:`local` (or
     copy it) before the ranks pass the next barrier, or alternate two instances.
+    Call :meth:`close` (all ranks) to unmap and free them.
     """
 
     def __init__(self, rows: int, heads: int, head_dim: int, dtype, device, head_offset: int = 0,
                  row_map=None, group=None):
+        import ctypes as C
         import torch.distributed as dist
+        from . import _lib
+        lib = _lib.load()
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         if self.world > 8:
             raise ValueError("at most 8 ranks")
-        self.local = torch.zeros((rows, heads, head_dim), dtype=dtype, device=device)
+        device = torch.device(device)
+        shape = (rows, heads, head_dim)
+        nbytes = rows * heads * head_dim * 2
+        self._lib, self._own, self._mapped = lib, None, []
         # Every rank runs the same collectives whatever happens locally, and all
         # ranks fail together if any of them could not export or map a buffer.
         ok, handle = 1, None
-        try:
-            handle = self.local.untyped_storage()._share_cuda_()
-        except Exception:
-            ok = 0
-        handles = [None] * self.world
-        dist.all_gather_object(handles, handle, group=group)
-        self.buffers = []
-        try:
+        with torch.cuda.device(device):
+            own = C.c_void_p()
+            if lib.la_peer_alloc(nbytes, C.byref(own)) == 0:
+                self._own = own.value
+                buf = C.create_string_buffer(64)
+                if lib.la_peer_export(self._own, buf) == 0:
+                    handle = buf.raw
+                else:
+                    ok = 0
+            else:
+                ok = 0
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle, group=group)
+            self.buffers = []
             for r, h in enumerate(handles):
-                if r == self.rank:
-                    self.buffers.append(self.local)
+                if r == self.rank and self._own is not None:
+                    self.buffers.append(_as_tensor(self._own, shape, dtype, device))
                     continue
-                # The handle is opened with THIS rank's GPU current (first tuple field),
-                # not the owner's: the mapping is then made for the GPU whose kernels
-                # will store through it, and the driver enables peer access to the owner.
-                storage = torch.UntypedStorage._new_shared_cuda(self.local.device.index, *h[1:])
-                t = torch.empty(0, dtype=dtype, device=self.local.device).set_(storage, 0, (rows, heads, head_dim))
-                self.buffers.append(t)
+                mapped = C.c_void_p()
+                # opened with THIS rank's GPU current: the mapping is made for the GPU whose
+                # kernels will store through it
+                if h is None or lib.la_peer_open(h, C.byref(mapped)) != 0:
+                    ok = 0
+                    continue
+                self._mapped.append(mapped.value)
+                self.buffers.append(_as_tensor(mapped.value, shape, dtype, device))
             torch.cuda.synchronize(device)
-        except Exception:
-            ok = 0
         flag = torch.tensor([ok], dtype=torch.int32, device=device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
         if int(flag.item()) == 0:
-            raise RuntimeError("peer-mapped output buffers are unavailable on at least one rank")
+            self.close(collective=False)
+            raise RuntimeError("peer-mapped output buffers are unavailable on at least one rank: " + _lib.last_error())
+        self.local = self.buffers[self.rank]
         self.head_offset = int(head_offset)
         self.rows = None
         if row_map is not None:
             self.rows = torch.as_tensor(list(row_map), dtype=torch.int32).to(device)
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self._device = device
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
@@ -191,3 +224,20 @@ class PeerOutput:
         """All ranks' kernels of the current step have finished (stream-ordered)."""
         import torch.distributed as dist
         dist.all_reduce(self._flag, group=self.group)
+
+    def close(self, collective: bool = True) -> None:
+        """Unmaps the peers' buffers, then (after a barrier, so that no peer still has this
+        rank's buffer mapped) frees this rank's own.  Tensors taken from :attr:`buffers`
+        must not be used afterwards."""
+        import torch.distributed as dist
+        self.buffers = []
+        self.local = None
+        for ptr in self._mapped:
+            self._lib.la_peer_close(ptr)
+        self._mapped = []
+        if collective:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+        if self._own is not None:
+            self._lib.la_peer_free(self._own)
+            self._own = None

@@ -622,3 +622,24 @@ def write_to_paged_cache(key, value, key_cache, value_cache, slot_mapping, kv_ca
             kt, vt = kt.clamp(-lim, lim), vt.clamp(-lim, lim)
         kc[blk, :, :, off, :] = kt.reshape(hkv, dx, x).to(kc.dtype)
         vc[blk, :, :, off] = vt.to(vc.dtype)
+
+
+# --------------------------------------------------------------------------
+# The query-only rotary op that precedes the attention op
+# --------------------------------------------------------------------------
+def apply_rotary_q(query, positions, cos_sin_cache):
+    """lazy_attn/lazy/model_executor/layers/rotary_embedding.py:40-66 (query path).
+
+    NeoX style on the full head: ``cos, sin = cos_sin_cache[positions].chunk(2)``;
+    ``o1 = x1*cos - x2*sin``, ``o2 = x2*cos + x1*sin`` over the two halves of each
+    head.  float32 math on float32 copies of the inputs; the result is rounded to
+    ``query.dtype`` (the op writes the query tensor in place).  The key is not
+    rotated: the attention kernels rotate the cached keys themselves.
+    """
+    q = query.to(torch.float32)
+    cs = cos_sin_cache.to(torch.float32)[positions.to(torch.long)]   # [T, rd]
+    half = cs.shape[-1] // 2
+    cos, sin = cs[:, None, :half], cs[:, None, half:]
+    x1, x2 = q[..., :half], q[..., half:2 * half]
+    out = torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin, q[..., 2 * half:]], dim=-1)
+    return out.to(query.dtype)

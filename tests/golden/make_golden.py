@@ -13,6 +13,9 @@ scheduler function is executed from its source text (its module cannot be
 imported against the vLLM version installed here) and the reference's
 ``max_rotation_offset`` is imported directly.
 
+``python tests/golden/make_golden.py int cos_sin backend`` regenerates only the named
+groups (the float group runs the Triton interpreter for minutes).
+
 The stored files are what the CPU tests pin the oracle with and what the GPU
 tests compare the CUDA kernels against; nothing at test time reads the
 reference checkout.
@@ -229,6 +232,67 @@ def gen_int():
     print("wrote metadata_vectors.json", len(rec))
 
 
+def gen_cos_sin():
+    """Rows of the reference's own llama3 cos/sin mirror (model_executor/rope/cos_sin.py:127-148),
+    for the geometries of the benchmark configurations."""
+    from lazy.model_executor.rope.cos_sin import llama3_cos_sin_torch
+    positions = [0, 1, 2, 17, 511, 4097, 65024, 65535, 131071]
+    data = {"positions": np.array(positions, dtype=np.int64),
+            "params": np.array([500000.0, 8.0, 1.0, 4.0, 8192.0], dtype=np.float64)}
+    for head in (64, 128):
+        cos, sin = zip(*[llama3_cos_sin_torch(pos, head, 500000.0, 8.0, 1.0, 4.0, 8192, "cpu") for pos in positions])
+        data[f"cos_{head}"] = torch.stack(cos).numpy()
+        data[f"sin_{head}"] = torch.stack(sin).numpy()
+    np.savez_compressed(HERE / "cos_sin_llama3.npz", **data)
+    print("wrote cos_sin_llama3.npz")
+
+
+def gen_backend_keywords():
+    """What the reference's attention backend imports and which keyword arguments it passes to
+    the two operators (backends/triton_attn.py), read from its source text: the patch-in test
+    binds the replacement operators against exactly these sets."""
+    import json
+    src = (REF / "lazy_attn/lazy/attention/backends/triton_attn.py").read_text()
+    tree = ast.parse(src)
+    imports = {}
+    for node in ast.walk(tree):
+        if isinstance(node, ast.ImportFrom) and node.module and "chunked_prefill_paged_decode" in node.module:
+            for alias in node.names:
+                imports[alias.asname or alias.name] = "." * node.level + node.module
+    common, updates = [], []
+    for node in ast.walk(tree):
+        if isinstance(node, ast.Assign) and isinstance(node.value, ast.Call) and \
+                getattr(node.value.func, "id", "") == "dict" and \
+                any(getattr(t, "id", "") == "kernel_kwargs" for t in node.targets):
+            common = [k.arg for k in node.value.keywords]
+    for node in ast.walk(tree):
+        if isinstance(node, ast.If):
+            for branch in (node.body, node.orelse):
+                upd, callee = None, None
+                for stmt in branch:
+                    call = stmt.value if isinstance(stmt, ast.Expr) and isinstance(stmt.value, ast.Call) else None
+                    if call is None:
+                        continue
+                    f = call.func
+                    if isinstance(f, ast.Attribute) and f.attr == "update" and getattr(f.value, "id", "") == "kernel_kwargs":
+                        upd = [k.arg for k in call.keywords]
+                    elif isinstance(f, ast.Name) and f.id.startswith("chunked_prefill_paged_decode"):
+                        callee = f.id
+                if upd is not None and callee is not None:
+                    updates.append((callee, upd))
+    rec = dict(imports=imports, common=common, extra={c: u for c, u in updates})
+    assert set(rec["extra"]) == {"chunked_prefill_paged_decode", "chunked_prefill_paged_decode_old"}, rec
+    (HERE / "backend_keywords.json").write_text(json.dumps(rec, indent=1))
+    print("wrote backend_keywords.json", {k: len(v) for k, v in rec["extra"].items()}, len(common))
+
+
 if __name__ == "__main__":
-    gen_int()
-    gen_float()
+    only = sys.argv[1:]
+    if not only or "int" in only:
+        gen_int()
+    if not only or "cos_sin" in only:
+        gen_cos_sin()
+    if not only or "backend" in only:
+        gen_backend_keywords()
+    if not only or "float" in only:
+        gen_float()

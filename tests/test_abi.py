@@ -25,7 +25,7 @@ def test_header_symbols_are_exported():
 
 def test_version_and_error_text():
     lib = _lib.load()
-    assert lib.la_version() == 100
+    assert lib.la_version() == 101
     assert isinstance(_lib.last_error(), str)
     assert lib.la_launch_count() >= 0
 
@@ -35,9 +35,8 @@ def test_struct_sizes_match_header():
     assert ctypes.sizeof(_lib.LaPrefillArgs) % 8 == 0
     assert ctypes.sizeof(_lib.LaDecodeArgs) % 8 == 0
     lib = _lib.load()
-    if hasattr(lib, "la_sizeof_prefill_args"):
-        assert lib.la_sizeof_prefill_args() == ctypes.sizeof(_lib.LaPrefillArgs)
-        assert lib.la_sizeof_decode_args() == ctypes.sizeof(_lib.LaDecodeArgs)
+    assert lib.la_sizeof_prefill_args() == ctypes.sizeof(_lib.LaPrefillArgs)
+    assert lib.la_sizeof_decode_args() == ctypes.sizeof(_lib.LaDecodeArgs)
 
 
 def test_null_arguments_are_refused_without_a_gpu():
@@ -47,6 +46,71 @@ def test_null_arguments_are_refused_without_a_gpu():
     assert lib.la_decode_fwd(None, None) == _lib.LA_ERR_INVALID_ARGUMENT
     assert lib.la_pack_block_table(None, None, None, None, None, 1, 1, 1, 1, None) == _lib.LA_ERR_INVALID_ARGUMENT
     assert lib.la_build_cos_sin_table(None, 0, 4, 8, 1e4, 0, 1.0, 1.0, 1.0, 8192, None) == _lib.LA_ERR_INVALID_ARGUMENT
+
+
+def _split_prefill_args():
+    """A call the tensor-core kernel accepts and splits over the KV range (64 CTAs of one row
+    block each against 148 SMs); the pointers are made up and never dereferenced on the host."""
+    a = _lib.LaPrefillArgs()
+    a.q = a.k = a.v = a.out = 0x10000
+    a.k_cache = a.v_cache = 0x20000
+    a.block_table = a.query_start_loc = a.seq_lens = 0x30000
+    a.q_stride_t, a.q_stride_h = 32 * 128, 128
+    a.k_stride_t, a.k_stride_h = 8 * 128, 128
+    a.v_stride_t, a.v_stride_h = 8 * 128, 128
+    a.o_stride_t, a.o_stride_h = 32 * 128, 128
+    a.kc_stride_block = a.vc_stride_block = 8 * 128 * 16
+    a.kc_stride_head = a.vc_stride_head = 128 * 16
+    a.num_blocks, a.table_stride = 4096, 520
+    a.batch, a.num_q_heads, a.num_kv_heads, a.head_dim = 8, 32, 8, 128
+    a.block_size, a.x, a.max_query_len, a.max_seq_len = 16, 8, 64, 8192
+    a.q_dtype = a.kv_dtype = _lib.DTYPE_BF16
+    a.rotary_dim, a.rot_mode, a.sm_scale = 128, _lib.ROT_LAZY, 0.088
+    return a
+
+
+def test_missing_workspace_is_an_error_not_a_slow_path():
+    """Automatic kernel selection never falls back to the general kernel because the
+    split-KV workspace is absent or short: the call fails with LA_ERR_WORKSPACE and says how
+    many bytes it needs (checked before anything touches the device, so it runs without a GPU)."""
+    lib = _lib.load()
+    a = _split_prefill_args()
+    need = lib.la_prefill_workspace_bytes(ctypes.byref(a))
+    assert need > 0, "pick a call that splits"
+    for kernel in (_lib.KERNEL_AUTO, _lib.KERNEL_TENSOR):
+        a.kernel = kernel
+        a.workspace, a.workspace_bytes = None, 0
+        assert lib.la_prefill_fwd(ctypes.byref(a), None) == _lib.LA_ERR_WORKSPACE
+        assert str(need) in _lib.last_error()
+        a.workspace, a.workspace_bytes = 0x40000, need - 1
+        assert lib.la_prefill_fwd(ctypes.byref(a), None) == _lib.LA_ERR_WORKSPACE
+    assert lib.la_prefill_fwd_noalloc(None, None) == _lib.LA_ERR_INVALID_ARGUMENT
+
+
+def test_patch_in_binds_what_the_reference_backend_passes():
+    """The keyword sets the reference backend passes to its two operators, and the modules it
+    imports them from, were read from its source when the fixtures were made
+    (tests/golden/backend_keywords.json, from lazy_attn/lazy/attention/backends/triton_attn.py):
+    the replacement operators must bind exactly those calls, so a rename in the reference
+    shows up when the fixture is regenerated."""
+    import inspect
+    import json
+    import types
+    from lazy_attention_b200 import vllm_patch
+    import lazy_attention_b200 as la
+
+    rec = json.loads((ROOT / "tests" / "golden" / "backend_keywords.json").read_text())
+    assert set(rec["imports"]) == {"chunked_prefill_paged_decode", "chunked_prefill_paged_decode_old"}
+    assert rec["imports"]["chunked_prefill_paged_decode"].endswith("ops.chunked_prefill_paged_decode")
+    assert rec["imports"]["chunked_prefill_paged_decode_old"].endswith("old_ops.chunked_prefill_paged_decode")
+    backend = types.ModuleType("fake_triton_attn")
+    previous = vllm_patch.install(backend)
+    for name, extra in rec["extra"].items():
+        fn = getattr(backend, name)
+        inspect.signature(fn).bind(**{k: None for k in rec["common"] + extra})
+    assert backend.chunked_prefill_paged_decode is la.chunked_prefill_paged_decode
+    assert backend.chunked_prefill_paged_decode_old is la.chunked_prefill_paged_decode_mepic
+    vllm_patch.uninstall(previous, backend)
 
 
 def test_patch_in_rebinds_backend_and_accepts_its_keywords():

@@ -331,6 +331,79 @@ def test_fused_cache_write_equals_separate_write(kernel, kv, variant, op):
     assert not torch.equal(kc_b, case["k_cache"]), "nothing was written"
 
 
+@pytest.mark.parametrize("geom", [synth.GEOM_1B, synth.GEOM_8B], ids=["d64", "d128"])
+@pytest.mark.parametrize("variant,op", [("lazy", "lazy_op"), ("mepic", "mepic_op")])
+def test_fused_rotary_op_on_the_query(geom, variant, op):
+    """``positions`` makes the kernels apply the query-only rotary op themselves: the result
+    must match the oracle run on a query that the op (oracle restatement, rounded to bf16)
+    has rotated beforehand, and the query tensor must be left as it was."""
+    import lazy_attention_b200 as la
+    reqs = [dict(docs=[2, 0, 1], qlen=37), dict(docs=[3, 1, 5], qlen=300), dict(docs=[1, 2, 4], qlen=1),
+            dict(docs=[0], qlen=16, lazy=False), dict(docs=[4, 3], qlen=1)]
+    case = synth.build_prefill(geom, torch.bfloat16, POOL, reqs, seed=10, variant=variant, device="cuda")
+    case["packed_block_table"] = util.pack_host(case).cuda()
+    g = torch.Generator().manual_seed(1)
+    rows = case["cos_sin_cache"].shape[0]
+    positions = torch.randint(0, rows, (case["q"].shape[0],), generator=g, dtype=torch.int64)
+    positions[3] = 0
+    rotated = dict(case)
+    rotated["q"] = oracle.apply_rotary_q(case["q"].cpu(), positions, case["cos_sin_cache"].cpu())
+    want = util.run_oracle(rotated, op)
+    q_before = case["q"].clone()
+    out = util.new_out(case)
+    fn = la.chunked_prefill_paged_decode if variant == "lazy" else la.chunked_prefill_paged_decode_mepic
+    kw = dict(is_lazy=case["is_lazy"], packed_block_table=case["packed_block_table"]) if variant == "lazy" else {}
+    fn(case["q"], case["k"], case["v"], out, "auto", case["k_cache"], case["v_cache"], case["block_table"],
+       case["query_start_loc"], case["seq_lens"], case["max_seq_len"], case["max_query_len"], case["k_scale"],
+       case["v_scale"], sm_scale=case["sm_scale"], cos_sin_cache=case["cos_sin_cache"], q_offset=case["q_offset"],
+       q_mask=case["q_mask"], kernel="tensor", positions=positions.cuda(), **kw)
+    torch.cuda.synchronize()
+    assert la.device_status() == 0
+    assert torch.equal(case["q"], q_before), "the query tensor was modified"
+    util.assert_close(out.float().cpu(), want, what=f"fused rotary {variant}", **HALF)
+    with pytest.raises(NotImplementedError, match="rotary"):
+        fn(case["q"], case["k"], case["v"], out, "auto", case["k_cache"], case["v_cache"], case["block_table"],
+           case["query_start_loc"], case["seq_lens"], case["max_seq_len"], case["max_query_len"], case["k_scale"],
+           case["v_scale"], sm_scale=case["sm_scale"], cos_sin_cache=case["cos_sin_cache"],
+           q_offset=case["q_offset"], q_mask=case["q_mask"], kernel="general", positions=positions.cuda(), **kw)
+
+
+@pytest.mark.parametrize("geom", [synth.GEOM_1B, synth.GEOM_8B], ids=["d64", "d128"])
+@pytest.mark.parametrize("kv", ["auto", "fp8_e4m3"])
+@pytest.mark.parametrize("llama3", [True, False], ids=["llama3", "plain"])
+def test_decode_computes_cos_sin_in_the_kernel(geom, kv, llama3, monkeypatch):
+    """LAZY_DECODE_COMPUTE_COS_SIN=1: the decode kernel takes cos/sin(position * inv_freq) from
+    the rotary layer's parameters instead of a table row.  Checked against the oracle with an
+    unrounded float32 table, and against the table path within the reference's own bound for
+    this switch (0.02 absolute, benchmarks/bench_rope_cos_sin.py:133)."""
+    import lazy_attention_b200 as la
+    docs = [[512] * 5, [500, 17, 1023], [16], [700, 700, 3], [33] * 9]
+    ks, vs = (0.09, 0.13) if "fp8" in kv else (1.0, 1.0)
+    case = synth.build_decode(geom, torch.bfloat16, docs, seed=24, device="cuda", kv_dtype=kv, k_scale=ks,
+                              v_scale=vs, llama3=llama3)
+    meta = dict(ROPE_TYPE=1 if llama3 else 0, BASE=geom.rope_theta, ORIG_MAX_POSITION=8192,
+                SCALING_FACTOR=8.0 if llama3 else 1.0, LOW_FACTOR=1.0, HIGH_FACTOR=4.0 if llama3 else 1.0)
+    table_out = util.run_cuda(case, "lazy_op", kernel="tensor")
+    exact = dict(case)
+    exact["cos_sin_cache"] = oracle.build_cos_sin_table(case["cos_sin_cache"].shape[0], geom.head_dim, geom.rope_theta,
+                                                        oracle.ROPE_LLAMA3 if llama3 else oracle.ROPE_DEFAULT,
+                                                        **(synth.LLAMA3_SCALING if llama3 else {}))
+    want = util.run_oracle(exact, "lazy_op")
+    monkeypatch.setenv("LAZY_DECODE_COMPUTE_COS_SIN", "1")
+    out = util.new_out(case)
+    la.chunked_prefill_paged_decode(case["q"], case["k"], case["v"], out, kv, case["k_cache"], case["v_cache"],
+                                    case["block_table"], case["query_start_loc"], case["seq_lens"],
+                                    case["max_seq_len"], 1, case["k_scale"], case["v_scale"],
+                                    sm_scale=case["sm_scale"], cos_sin_cache=None, rope_meta=meta,
+                                    is_lazy=case["is_lazy"], q_offset=case["q_offset"], q_mask=case["q_mask"],
+                                    packed_block_table=case["packed_block_table"], kernel="tensor")
+    torch.cuda.synchronize()
+    assert la.device_status() == 0
+    got = out.float().cpu()
+    util.assert_close(got, want, what="in-kernel cos/sin vs oracle", **(FP8 if "fp8" in kv else HALF))
+    assert float((got - table_out).abs().max()) < 0.02, "computed and loaded cos/sin disagree"
+
+
 def test_empty_batch_and_skip_decode_leave_output_untouched():
     import lazy_attention_b200 as la
     case = util.to_device(util.load_golden("lazy_prefill_small"), "cuda")

@@ -126,3 +126,25 @@ def test_slice_case_matches_whole_case():
             (s0, s1), (h0, h1) = sub["token_range"], sub["head_range"]
             got = util.run_oracle(sub, op)
             assert float((got - whole[s0:s1, h0:h1]).abs().max()) < 1e-5
+
+
+def test_cos_sin_table_matches_reference_mirror():
+    """The oracle's llama3 table against rows of the reference's own torch mirror
+    (lazy_attn/lazy/model_executor/rope/cos_sin.py:127-148), stored by make_golden.py."""
+    z = np.load(util.GOLDEN / "cos_sin_llama3.npz")
+    base, factor, low, high, orig = (float(v) for v in z["params"])
+    positions = [int(v) for v in z["positions"]]
+    for head in (64, 128):
+        table = oracle.build_cos_sin_table(max(positions) + 1, head, base, oracle.ROPE_LLAMA3, factor, low, high,
+                                           int(orig))
+        rows = table[positions]
+        half = head // 2
+        # the mirror returns the NeoX-duplicated layout [head]; the table keeps one half each
+        want_cos, want_sin = torch.from_numpy(z[f"cos_{head}"]), torch.from_numpy(z[f"sin_{head}"])
+        assert torch.equal(want_cos[:, :half], want_cos[:, half:])
+        # float32 evaluation order differs slightly (theta = pos * inv): a few ulp of the angle
+        assert float((rows[:, :half] - want_cos[:, :half]).abs().max()) < 2e-3
+        assert float((rows[:, half:] - want_sin[:, :half]).abs().max()) < 2e-3
+        small = [i for i, pos in enumerate(positions) if pos <= 4097]
+        assert float((rows[small][:, :half] - want_cos[small][:, :half]).abs().max()) < 1e-6
+        assert float((rows[small][:, half:] - want_sin[small][:, :half]).abs().max()) < 1e-6

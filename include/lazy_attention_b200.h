@@ -365,6 +365,12 @@ int64_t la_launch_count(void);
  * (0 = none) and clears it.  A negative value is an LA_ERR_* of the call itself. */
 int la_device_status(void);
 
+/* The same check as a status: synchronises the device and returns LA_OK, or
+ * LA_ERR_DEVICE_STATUS with the code in la_last_error() (the word is cleared).  The kernels
+ * never report through the calls that launched them (those do not synchronise): an
+ * integration polls one of these two, e.g. once per engine step. */
+int la_check_device(void);
+
 /* sizeof(LaPrefillArgs) / sizeof(LaDecodeArgs) as compiled into the library, so
  * that a foreign-function binding can verify its mirror of the structs. */
 size_t la_sizeof_prefill_args(void);

@@ -25,7 +25,7 @@ from .cache import write_to_paged_cache
 from .attention import (chunked_prefill_paged_decode,
                         chunked_prefill_paged_decode_mepic,
                         context_attention_fwd, context_attention_fwd_mepic,
-                        device_status, launch_count, reserve_workspace)
+                        check_device, device_status, launch_count, reserve_workspace)
 
 __all__ = [
     "reserve_workspace",
@@ -35,5 +35,5 @@ __all__ = [
     "ROPE_LLAMA3", "build_cos_sin_table", "rope_meta_from_layer",
     "chunked_prefill_paged_decode", "chunked_prefill_paged_decode_mepic",
     "context_attention_fwd", "context_attention_fwd_mepic", "launch_count",
-    "device_status", "write_to_paged_cache",
+    "device_status", "check_device", "write_to_paged_cache",
 ]

@@ -25,7 +25,7 @@ EXPORTS = (
     "la_build_cos_sin_table", "la_last_error", "la_version", "la_launch_count",
     "la_sizeof_prefill_args", "la_sizeof_decode_args", "la_device_status",
     "la_prefill_fwd_noalloc", "la_write_paged_cache",
-    "la_peer_alloc", "la_peer_export", "la_peer_open", "la_peer_close", "la_peer_free",
+    "la_check_device", "la_peer_alloc", "la_peer_export", "la_peer_open", "la_peer_close", "la_peer_free",
 )
 
 
@@ -159,6 +159,8 @@ def load() -> C.CDLL:
     lib.la_launch_count.restype = C.c_int64
     lib.la_device_status.argtypes = []
     lib.la_device_status.restype = C.c_int
+    lib.la_check_device.argtypes = []
+    lib.la_check_device.restype = C.c_int
     lib.la_peer_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]
     lib.la_peer_export.argtypes = [C.c_void_p, C.c_char_p]
     lib.la_peer_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]

@@ -38,6 +38,14 @@ def device_status() -> int:
     return int(_lib.load().la_device_status())
 
 
+def check_device() -> None:
+    """Synchronise and raise ``RuntimeError`` if a kernel of this library gave up on a
+    bounded wait since the last check (its results are then invalid).  The operators do
+    not synchronise, so they cannot report this themselves: an engine that uses the
+    patch-in calls this once per step, or every few steps."""
+    _lib.check(_lib.load().la_check_device(), "la_check_device")
+
+
 def launch_count() -> int:
     """Kernels launched by the library in this process."""
     return int(_lib.load().la_launch_count())

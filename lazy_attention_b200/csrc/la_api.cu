@@ -232,6 +232,14 @@ extern "C" int la_device_status(void) {
   return host[0];
 }
 
+extern "C" int la_check_device(void) {
+  const int code = la_device_status();
+  if (code < 0) return code;  // the query itself failed
+  LA_REQUIRE(code == 0, LA_ERR_DEVICE_STATUS,
+             "a kernel gave up on a bounded wait (code %d): results of calls since the last check are invalid", code);
+  return LA_OK;
+}
+
 // ---- buffers of the fused output gather, shared across processes with CUDA IPC ---------------
 extern "C" int la_peer_alloc(size_t bytes, void** out) {
   LA_REQUIRE(out != nullptr && bytes > 0, LA_ERR_INVALID_ARGUMENT, "la_peer_alloc: null result or zero size");

@@ -194,9 +194,9 @@ class LazyMetadataBuffers:
             if q_offset is not None:
                 if len(q_offset) and max(q_offset) > MAX_PACKED_Q_OFFSET:
                     raise ValueError(
-                        f"Request {getattr(req, 'req_id', idx)} needs a rotation offset of "
-                        f"{max(q_offset)}, past the {MAX_PACKED_Q_OFFSET} the packed block "
-                        f"table's 16-bit field holds; it should have been refused at admission.")
+                        f"request {getattr(req, 'req_id', idx)}: q_offset {max(q_offset)} does not fit the "
+                        f"16 bits the packed block table gives it (limit {MAX_PACKED_Q_OFFSET}); packing it "
+                        f"would overwrite the block id, so the request must be rejected before it is scheduled")
                 self.lazy_offset_np[idx, :len(q_offset)] = q_offset
             if q_mask is not None:
                 self.lazy_mask_np[idx, :len(q_mask)] = q_mask

@@ -9,6 +9,12 @@ functions, which accept the same keyword set; ``uninstall`` restores them.
 This is the `PatchTarget` pair a maintainer would register in
 lazy_attn/lazy/vllm_patch.py:79-110, in a form that also works on an already
 imported module.
+
+The operators enqueue their kernels and return, like the reference's; a kernel whose
+bounded wait expired (a logic error, never seen in normal operation) can therefore only
+report through the device status word.  An engine that installs this patch should call
+``lazy_attention_b200.check_device()`` once per step or every few steps: it synchronises,
+and raises if any call since the last check produced invalid results.
 """
 from __future__ import annotations
 

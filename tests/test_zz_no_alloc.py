@@ -6,8 +6,8 @@ cudaMalloc's device-wide synchronisation is not acceptable -- so they cannot
 supply the split-KV scratch.  ``la_prefill_fwd_noalloc`` keeps that scratch in a
 fixed 32 MiB array inside the library.  This test drives it through the C ABI on
 a call that really splits the KV range, twice in a row (the array keeps the
-first call's contents), and checks both results against ``la_prefill_fwd``
-within the tolerance the other bf16 tests use.  It also checks that a call too
+first call's contents), and checks both results against ``la_prefill_fwd`` and
+against the CPU oracle within the tolerance the other bf16 tests use.  It also checks that a call too
 large for the array is refused with a message that names both sizes.
 
 The file sorts last on purpose: with ``pytest -x`` every other test has run
@@ -41,6 +41,7 @@ def test_no_alloc_entry_matches_regular_entry_twice():
     # kernel splits the KV range and goes through the scratch.
     case = synth.config_c2(device="cuda")
     want = util.run_cuda(case, "lazy_prefill", kernel="tensor")
+    truth = util.run_oracle(case, "lazy_prefill")
     for attempt in range(2):
         out = torch.full((case["num_tokens"], 32, 64), float("nan"), dtype=torch.bfloat16, device="cuda")
         held = torch.cuda.memory_allocated()
@@ -48,6 +49,7 @@ def test_no_alloc_entry_matches_regular_entry_twice():
         assert torch.cuda.memory_allocated() == held, "the entry point went through torch's allocator"
         assert la.device_status() == 0
         util.assert_close(out.float().cpu(), want, what=f"no-alloc call {attempt}", **HALF)
+        util.assert_close(out.float().cpu(), truth, what=f"no-alloc call {attempt} vs oracle", **HALF)
     # a different call in between must not disturb the next one
     other = synth.build_prefill(synth.GEOM_8B, torch.bfloat16, [512] * 4, [dict(docs=[3, 1, 0, 2], qlen=64)],
                                 seed=5, device="cuda")

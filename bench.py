@@ -76,6 +76,9 @@ def parse_args():
                          "e4m3 for c5)")
     ap.add_argument("--scale", type=float, default=1.0,
                     help="shrink the workload (profiling captures only; not a bench value)")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="on ONE GPU, run the shard a rank of an N-GPU job would get (tuning aid for the "
+                         "per-rank kernel; not a bench value)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="only the headline workload")
@@ -481,7 +484,11 @@ def run_workload(name, args, world, rank, local_rank, device):
     import lazy_attention_b200 as la
     from lazy_attention_b200 import sharding
 
-    case, info = build_workload(name, device, args.variant, rank, world, args.scale, args.kv_dtype)
+    if world == 1 and args.shard_of > 1:
+        case, info = build_workload(name, device, args.variant, 0, args.shard_of, args.scale, args.kv_dtype)
+        info = dict(info, partition=f"rank 0's shard of {args.shard_of} ({info['partition']}), run alone")
+    else:
+        case, info = build_workload(name, device, args.variant, rank, world, args.scale, args.kv_dtype)
     flops, byts, units = algorithmic_work(case, info)
     step, out = make_step(case, info, args.kernel)
     g = case["geom"]
@@ -731,7 +738,7 @@ def run_workload(name, args, world, rank, local_rank, device):
                roofline=roof, e2e=e2e, gpu_launches=launches_timed, clocks=clk.summary())
     if gather_check is not None:
         res["gather_check"] = gather_check
-    if world == 1 and not args.no_triton and args.scale == 1.0:
+    if world == 1 and not args.no_triton and args.scale == 1.0 and args.shard_of == 1:
         tb = triton_baseline(case, info, fast_step())
         if "ms_per_step" in tb:
             tb["value"] = tokens_all / (tb["ms_per_step"] * 1e-3)
@@ -764,7 +771,8 @@ def main():
     head = run_workload(args.workload, args, world, rank, local_rank, device)
     torch.cuda.empty_cache()
     also = {}
-    if not args.no_also and args.scale == 1.0 and args.workload == "c4" and args.kv_dtype == "auto":
+    if not args.no_also and args.scale == 1.0 and args.workload == "c4" and args.kv_dtype == "auto" \
+            and args.shard_of == 1:
         for name in ["c5"] + (["c3"] if world == 1 else []):
             r = run_workload(name, args, world, rank, local_rank, device)
             torch.cuda.empty_cache()

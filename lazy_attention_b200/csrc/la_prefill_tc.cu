@@ -1540,21 +1540,28 @@ TcPlan make_plan(const LaPrefillArgs& a) {
   }
   if (pl.pair) pl.mblocks = (pl.mblocks + 1) & ~1;
   pl.rows_cap = (int64_t)pl.mblocks * kRowsPerCta;
-  // Split the KV range when the row blocks alone cannot fill the GPU.  The
-  // sequence lengths live on the device, so the plan uses the caller's maxima.
+  // Split the KV range when the row blocks alone cannot fill the GPU.  The sequence
+  // lengths live on the device, so the plan uses the caller's maxima.  Cost of a split
+  // count s, in units of one tile step of a CTA: the grid runs in waves over the SMs (one
+  // CTA, or half a pair, per SM); a CTA costs its tiles plus a fixed part (staging Q, the
+  // first tile's latency, reading the accumulator out: about six tile steps); the merge
+  // kernel streams s partial rows per output row.  The constants come from sweeps of the
+  // split count on the 8B configuration at 1/1, 1/2, 1/4 and 1/8 of its heads, whose
+  // measured order this model reproduces.
   const int64_t ctas = (int64_t)pl.mblocks * a.num_kv_heads * a.batch;
   int64_t max_seq = a.max_seq_len > 0 ? a.max_seq_len : 0;
   const int64_t tiles = (max_seq + kTileN - 1) / kTileN + 1;
+  const int64_t units = pl.pair ? ctas / 2 : ctas;
+  const int64_t slots = pl.pair ? 74 : 148;
+  const double merge_per_split = 2.8 * (double)(pl.rows_cap * a.num_kv_heads * a.batch) / 16384.0;
   int best = 1;
-  double best_eff = 0.0;
-  const int kSms = 148;
+  double best_cost = 0.0;
   for (int s = 1; s <= 16; ++s) {
     if (s > 1 && tiles / s < 4) break;
-    const int64_t n = ctas * s;
-    const double eff = (double)n / (double)(((n + kSms - 1) / kSms) * kSms);
-    const double score = eff - 0.01 * (s - 1);  // each split adds combine traffic
-    if (score > best_eff + 1e-9) {
-      best_eff = score;
+    const int64_t waves = (units * s + slots - 1) / slots;
+    const double cost = (double)waves * (double)((tiles + s - 1) / s + 6) + (s > 1 ? merge_per_split * s : 0.0);
+    if (s == 1 || cost < best_cost - 1e-9) {
+      best_cost = cost;
       best = s;
     }
   }

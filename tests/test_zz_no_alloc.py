@@ -62,9 +62,11 @@ def test_no_alloc_entry_matches_regular_entry_twice():
     util.assert_close(out3.float().cpu(), want, what="no-alloc after another shape", **HALF)
 
 
-def test_no_alloc_entry_refuses_what_does_not_fit():
+def test_no_alloc_entry_refuses_what_does_not_fit(monkeypatch):
     from lazy_attention_b200 import no_alloc
-    # Five requests of that shape split just as finely and need five times the scratch.
+    # Five requests of that shape, with the split count pinned to 8 (the library's tuning
+    # switch; the planner itself would not split a batch this wide): 43 MB of partials.
+    monkeypatch.setenv("LAZY_ATTN_B200_PREFILL_SPLITS", "8")
     pool = [512] * 50
     reqs = [dict(docs=list(range(10 * b, 10 * b + 10)), qlen=128) for b in range(5)]
     case = synth.build_prefill(synth.GEOM_1B, torch.bfloat16, pool, reqs, seed=2, device="cuda")

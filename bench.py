@@ -16,8 +16,9 @@ BASELINE configurations (seeded synthetic inputs of their shapes):
 
 One JSON line is printed by rank 0: the headline workload (c4 unless
 ``--workload`` says otherwise) with, under ``also``, the decode workload c5 at
-the same N (sharded by request) and, at N = 1, the ragged prefill workload c3,
-each with its own value, roofline and end-to-end figure.  At N = 1 the line
+the same N (sharded by request) and, at N = 1, the ragged prefill workload c3 and
+the small one c2 (the prefill shape the reference's Triton kernel compiles for on
+this GPU), each with its own value, roofline and end-to-end figure.  At N = 1 the line
 also carries ``triton_baseline``: the reference's own Triton kernels compiled
 for this GPU and timed on the same inputs (outside every timed region of this
 library).  At N > 1 one step of the output gather fused into the kernels is
@@ -773,7 +774,7 @@ def main():
     also = {}
     if not args.no_also and args.scale == 1.0 and args.workload == "c4" and args.kv_dtype == "auto" \
             and args.shard_of == 1:
-        for name in ["c5"] + (["c3"] if world == 1 else []):
+        for name in ["c5"] + (["c3", "c2"] if world == 1 else []):
             r = run_workload(name, args, world, rank, local_rank, device)
             torch.cuda.empty_cache()
             also[name] = {k: r[k] for k in ("value", "unit", "ms_per_step", "tokens_per_step", "dtype", "config",

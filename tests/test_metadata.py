@@ -65,7 +65,7 @@ def test_buffers_accept_limit_and_refuse_overflow():
     buf.refresh([_req([1, la.MAX_PACKED_Q_OFFSET])])
     assert int(buf.lazy_offset_np[0, 1]) == la.MAX_PACKED_Q_OFFSET
     assert bool(buf.is_lazy_req[0]) and int(buf.lazy_offset[0, 1]) == la.MAX_PACKED_Q_OFFSET
-    with pytest.raises(ValueError, match="past the"):
+    with pytest.raises(ValueError, match="does not fit the 16 bits"):
         buf.refresh([_req([1, la.MAX_PACKED_Q_OFFSET + 1])])
 
 

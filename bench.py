@@ -87,6 +87,10 @@ def parse_args():
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: 'fused' = the kernels store their result rows into every rank's output "
                          "buffer (peer-mapped memory) and the step ends with a barrier; 'nccl' = all-gather")
+    ap.add_argument("--barrier", default="signal", choices=["signal", "nccl"],
+                    help="how a step of the fused gather ends: 'signal' = the library's own kernel (every rank "
+                         "announces itself in its peers' signal buffers and waits for theirs), 'nccl' = a "
+                         "one-element all-reduce")
     ap.add_argument("--cuda-graph", default="on", choices=["on", "off"],
                     help="replay the library's launches of one call from a CUDA graph in the device-resident "
                          "timing (the end-to-end leg always launches eagerly)")
@@ -521,7 +525,8 @@ def run_workload(name, args, world, rank, local_rank, device):
                 mk = lambda: sharding.PeerOutput(info["total_seqs"], g.num_q_heads, g.head_dim, out.dtype,  # noqa: E731
                                                  device, row_map=case["global_rows"])
             peers = [mk(), mk()]  # two sets: a step's result is read while the next step is written
-            gather_mode = "fused into the kernels (peer stores over NVLink) + barrier"
+            gather_mode = "fused into the kernels (peer stores over NVLink) + " + (
+                "signal kernel" if args.barrier == "signal" else "one-element all-reduce")
         except Exception as e:
             peers = None
             gather_mode = f"nccl all-gather (peer buffers unavailable: {type(e).__name__})"
@@ -537,7 +542,7 @@ def run_workload(name, args, world, rank, local_rank, device):
             torch.cuda.synchronize(device)
             dist.barrier()
             step(peer_out=pset)
-            pset.barrier()
+            pset.barrier(collective=True if args.barrier == "nccl" else None)
             torch.cuda.synchronize(device)
             ok &= int(torch.equal(pset.local, want))
         flag = torch.tensor([ok], dtype=torch.int32, device=device)
@@ -580,7 +585,7 @@ def run_workload(name, args, world, rank, local_rank, device):
 
     if peers is not None:
         def post(o, slot=0):
-            peers[slot].barrier()
+            peers[slot].barrier(collective=True if args.barrier == "nccl" else None)
             return peers[slot].local
     elif world > 1:
         def post(o, slot=0):

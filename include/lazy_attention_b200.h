@@ -343,13 +343,25 @@ int la_write_paged_cache(const LaWriteCacheArgs* args, void* stream);
  *                   (the device whose kernels will store through the mapping)
  *   la_peer_close   unmaps a pointer from la_peer_open
  *   la_peer_free    frees a buffer from la_peer_alloc (after every peer has closed it)
+ *   la_peer_barrier one small kernel on `stream` that ends the step of a fused gather: it tells
+ *                   every rank "my kernels before this point have finished, their stores into your
+ *                   buffer have landed" and returns once every rank has said so.  `signals[r]` is
+ *                   rank r's signal buffer (LA_PEER_SIGNAL_BYTES from la_peer_alloc, own or
+ *                   mapped with la_peer_open; never written by anything else).  Every rank must
+ *                   call it the same number of times (the round counter lives in the buffer, so a
+ *                   captured launch can be replayed).  One process per GPU: ranks that share a GPU
+ *                   must not use it (their kernels would wait on one another on one device).  The
+ *                   wait is bounded (about 4 s of GPU clock); a rank that never arrives leaves
+ *                   LA_ERR_DEVICE_STATUS for la_device_status() and the kernel returns.
  */
 #define LA_IPC_HANDLE_BYTES 64
+#define LA_PEER_SIGNAL_BYTES 256
 int la_peer_alloc(size_t bytes, void** out);
 int la_peer_export(const void* buffer, unsigned char handle[LA_IPC_HANDLE_BYTES]);
 int la_peer_open(const unsigned char handle[LA_IPC_HANDLE_BYTES], void** out);
 int la_peer_close(void* mapped);
 int la_peer_free(void* buffer);
+int la_peer_barrier(void* const* signals, int32_t world, int32_t rank, void* stream);
 
 /* Text of the last error on this thread ("" if none). */
 const char* la_last_error(void);

@@ -25,11 +25,12 @@ EXPORTS = (
     "la_build_cos_sin_table", "la_last_error", "la_version", "la_launch_count",
     "la_sizeof_prefill_args", "la_sizeof_decode_args", "la_device_status",
     "la_prefill_fwd_noalloc", "la_write_paged_cache",
-    "la_check_device", "la_peer_alloc", "la_peer_export", "la_peer_open", "la_peer_close", "la_peer_free",
+    "la_check_device", "la_peer_alloc", "la_peer_export", "la_peer_open", "la_peer_close", "la_peer_free", "la_peer_barrier",
 )
 
 
 LA_MAX_PEERS = 8
+LA_PEER_SIGNAL_BYTES = 256
 
 
 class LaPeerOut(C.Structure):
@@ -166,7 +167,9 @@ def load() -> C.CDLL:
     lib.la_peer_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
     lib.la_peer_close.argtypes = [C.c_void_p]
     lib.la_peer_free.argtypes = [C.c_void_p]
-    for fn in (lib.la_peer_alloc, lib.la_peer_export, lib.la_peer_open, lib.la_peer_close, lib.la_peer_free):
+    lib.la_peer_barrier.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p]
+    for fn in (lib.la_peer_alloc, lib.la_peer_export, lib.la_peer_open, lib.la_peer_close, lib.la_peer_free,
+               lib.la_peer_barrier):
         fn.restype = C.c_int
     lib.la_sizeof_prefill_args.restype = C.c_size_t
     lib.la_sizeof_decode_args.restype = C.c_size_t

@@ -322,8 +322,10 @@ def context_attention_fwd_mepic(q, k, v, o, kv_cache_dtype: str, k_cache, v_cach
                                 force_fp32_rotary: bool = False, kernel=None, peer_out=None,
                                 packed_block_table=None, slot_mapping=None, positions=None):
     """Prefix-prefill attention, per-token rotation variant: cached K is rotated
-    at each token's slot position, new K at ``ctx_len + n``.  The rotation is
-    always evaluated in float32 (``force_fp32_rotary`` is accepted and implied)."""
+    at each token's slot position, new K at ``ctx_len + n``.  The tensor-core
+    kernels evaluate the rotation in packed 16-bit arithmetic (the reference's
+    default), the general kernel in float32; ``force_fp32_rotary`` is accepted and
+    does not change the kernel -- the two evaluations differ by rounding only."""
     _prefill(q, k, v, o, kv_cache_dtype, k_cache, v_cache, b_loc, b_start_loc, b_seq_len,
              max_seq_len, max_input_len, k_scale, v_scale, alibi_slopes, sliding_window,
              sm_scale, skip_decode, cos_sin_cache, rotary_dim, is_neox_style, None,

@@ -2,6 +2,7 @@
 #include <cstring>
 
 #include "la_common.cuh"
+#include "la_sm100.cuh"
 
 namespace la {
 
@@ -279,6 +280,67 @@ extern "C" int la_peer_open(const unsigned char handle[LA_IPC_HANDLE_BYTES], voi
 extern "C" int la_peer_close(void* mapped) {
   if (mapped == nullptr) return LA_OK;
   LA_CHECK_CUDA(cudaIpcCloseMemHandle(mapped));
+  return LA_OK;
+}
+
+// ---- end-of-step barrier of the fused gather -------------------------------------------------
+// Signal buffer of a rank (LA_PEER_SIGNAL_BYTES, zero at allocation): word r = the last round
+// rank r has announced to this rank, word kRoundWord = this rank's own round counter.
+namespace la {
+namespace {
+constexpr int kRoundWord = 32;
+constexpr uint64_t kBarrierLimitNs = 4000ull * 1000 * 1000;
+struct PeerSignals {
+  uint32_t* ptr[LA_MAX_PEERS];
+};
+
+__global__ void peer_barrier_kernel(PeerSignals s, int world, int rank, int* status) {
+  const int lane = threadIdx.x;
+  uint32_t* mine = s.ptr[rank];
+  const uint32_t round = *reinterpret_cast<volatile uint32_t*>(mine + kRoundWord) + 1u;
+  __syncwarp();
+  if (lane == 0) *reinterpret_cast<volatile uint32_t*>(mine + kRoundWord) = round;
+  if (lane >= world) return;
+  // The kernels launched before this one on the stream have completed, so their stores into
+  // the peers' buffers have been performed; the fence orders this thread's announcement
+  // after them for an observer on another GPU.
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(s.ptr[lane] + rank), "r"(round) : "memory");
+  const uint32_t* from = mine + lane;
+  uint64_t t0 = 0;
+  uint32_t polls = 0;
+  while (true) {
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(from) : "memory");
+    // a rank can be one round ahead (it has passed this barrier and reached the next)
+    if ((int32_t)(seen - round) >= 0) break;
+    if ((++polls & 63u) == 0) {
+      const uint64_t now = sm100::global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kBarrierLimitNs) {
+        if (status) atomicCAS(status, 0, 300 + lane);  // rank `lane` never arrived
+        break;
+      }
+    }
+  }
+}
+}  // namespace
+}  // namespace la
+
+extern "C" int la_peer_barrier(void* const* signals, int32_t world, int32_t rank, void* stream) {
+  LA_REQUIRE(signals != nullptr, LA_ERR_INVALID_ARGUMENT, "la_peer_barrier: null signals");
+  LA_REQUIRE(world >= 1 && world <= LA_MAX_PEERS && rank >= 0 && rank < world, LA_ERR_INVALID_ARGUMENT,
+             "la_peer_barrier: rank %d of %d (at most %d ranks)", rank, world, LA_MAX_PEERS);
+  la::PeerSignals s;
+  for (int r = 0; r < LA_MAX_PEERS; ++r) s.ptr[r] = nullptr;
+  for (int r = 0; r < world; ++r) {
+    LA_REQUIRE(signals[r] != nullptr && (reinterpret_cast<uintptr_t>(signals[r]) & 3) == 0, LA_ERR_INVALID_ARGUMENT,
+               "la_peer_barrier: signal buffer of rank %d is null or unaligned", r);
+    s.ptr[r] = reinterpret_cast<uint32_t*>(signals[r]);
+  }
+  la::peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(s, world, rank, la::device_status_ptr());
+  LA_CHECK_CUDA(cudaGetLastError());
+  la::count_launch();
   return LA_OK;
 }
 

@@ -181,6 +181,31 @@ __device__ __forceinline__ float rope_inv_freq(const DecParams& p, int i) {
   return (1.f - smooth) * inv / p.rope_factor + smooth * inv;
 }
 
+// Forward rotation of two packed key pairs (dims d, d+1 and their partners D/2 further) in the
+// MMA's own 16-bit type: k1' = k1*c - k2*s, k2' = k1*s + k2*c, two roundings per result as the
+// reference's 16-bit evaluation has (old_ops/chunked_prefill_paged_decode.py:228-229).
+template <bool BF16MMA>
+__device__ __forceinline__ void rotate_pair(uint32_t& k1, uint32_t& k2, uint32_t c, uint32_t s) {
+  const uint32_t nk2 = k2 ^ 0x80008000u;
+  if constexpr (BF16MMA) {
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&k1), b = *reinterpret_cast<const __nv_bfloat162*>(&k2);
+    const __nv_bfloat162 nb = *reinterpret_cast<const __nv_bfloat162*>(&nk2);
+    const __nv_bfloat162 cc = *reinterpret_cast<const __nv_bfloat162*>(&c), ss = *reinterpret_cast<const __nv_bfloat162*>(&s);
+    const __nv_bfloat162 r1 = __hfma2(nb, ss, __hmul2(a, cc));
+    const __nv_bfloat162 r2 = __hfma2(a, ss, __hmul2(b, cc));
+    k1 = *reinterpret_cast<const uint32_t*>(&r1);
+    k2 = *reinterpret_cast<const uint32_t*>(&r2);
+  } else {
+    const __half2 a = *reinterpret_cast<const __half2*>(&k1), b = *reinterpret_cast<const __half2*>(&k2);
+    const __half2 nb = *reinterpret_cast<const __half2*>(&nk2);
+    const __half2 cc = *reinterpret_cast<const __half2*>(&c), ss = *reinterpret_cast<const __half2*>(&s);
+    const __half2 r1 = __hfma2(nb, ss, __hmul2(a, cc));
+    const __half2 r2 = __hfma2(a, ss, __hmul2(b, cc));
+    k1 = *reinterpret_cast<const uint32_t*>(&r1);
+    k2 = *reinterpret_cast<const uint32_t*>(&r2);
+  }
+}
+
 // One output element: to `out`, or with the fused gather to the same place of every rank's buffer.
 template <bool BF16>
 __device__ __forceinline__ void store_result(const DecParams& p, int row_q, int head, int d, float val) {
@@ -521,17 +546,13 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
             const uint32_t cw[4] = {cl.x, ch.x, cl.y, ch.y}, sw[4] = {sl.x, sh.x, sl.y, sh.y};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              float2 a, b;
-              if constexpr (BF16MMA) {
-                a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&k1[e]));
-                b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&k2[e]));
-              } else {
-                a = __half22float2(*reinterpret_cast<__half2*>(&k1[e]));
-                b = __half22float2(*reinterpret_cast<__half2*>(&k2[e]));
+              uint32_t cv = cw[e], sv = sw[e];
+              if constexpr (BF16 && !BF16MMA) {  // bf16 table, keys and MMAs in f16 (fp8 cache)
+                const float2 cc = unpack_q<true>(cv), ss = unpack_q<true>(sv);
+                cv = pack_mma<false>(cc.x, cc.y);
+                sv = pack_mma<false>(ss.x, ss.y);
               }
-              const float2 cc = unpack_q<BF16>(cw[e]), ss = unpack_q<BF16>(sw[e]);
-              k1[e] = pack_mma<BF16MMA>(a.x * cc.x - b.x * ss.x, a.y * cc.y - b.y * ss.y);
-              k2[e] = pack_mma<BF16MMA>(a.x * ss.x + b.x * cc.x, a.y * ss.y + b.y * cc.y);
+              rotate_pair<BF16MMA>(k1[e], k2[e], cv, sv);
             }
             mma16816<BF16MMA>(s[i], k1[0], k1[1], k1[2], k1[3], qcur[ks][0], qcur[ks][1]);
             mma16816<BF16MMA>(s[i], k2[0], k2[1], k2[2], k2[3], qcur[ks + KSTEPS / 2][0], qcur[ks + KSTEPS / 2][1]);

@@ -802,11 +802,12 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
         const float inv = l_row > 0.f ? out_scale / l_row : 0.f;
         uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
                         ((int64_t)(s0 + tq) * p.o_st + (int64_t)head * p.o_sh) * 2;
-        int64_t peer_off = 0;  // byte offset of this thread's row in every rank's buffer
-        if (p.peer.num_peers > 0 && row_valid) {
-          const int64_t prow = p.peer.rows ? p.peer.rows[s0 + tq] : (s0 + tq);
-          peer_off = (prow * p.peer.stride_t + (int64_t)(p.peer.head_offset + head) * p.peer.stride_h) * 2;
-        }
+        // Fused gather: the warp's 32 rows go through shared memory (the Q tiles are no longer
+        // read once every MMA has completed) so that a row leaves as one contiguous run of
+        // 16-byte stores; one row per thread would cross the link as 16-byte pieces.
+        constexpr int kRowBytes = D * 2, kRowChunks = kRowBytes / 16;
+        const bool to_peers = p.peer.num_peers > 0;
+        uint8_t* stage_rows = sQ + (t * 128 + qd * 32) * kRowBytes;
 #pragma unroll 1
         for (int ch = 0; ch < D / 32; ++ch) {
           uint32_t o[32];
@@ -817,16 +818,36 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
 #pragma unroll
           for (int i = 0; i < 32; i += 2)
             pw[i >> 1] = pack2<BF16>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-          if (row_valid) {
-            if (p.peer.num_peers == 0) {
+          if (to_peers) {
+            // chunk c of row `lane` sits at slot c ^ (lane mod chunks): eight lanes hit eight
+            // different 16-byte bank groups on the way in and on the way out
 #pragma unroll
-              for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(orow + ch * 64 + i * 16) = w[i];
-            } else {
-              for (int q = 0; q < p.peer.num_peers; ++q) {
-                uint8_t* dst = reinterpret_cast<uint8_t*>(p.peer.out[q]) + peer_off + ch * 64;
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<uint4*>(stage_rows + lane * kRowBytes +
+                                        (((ch * 4 + i) ^ (lane & (kRowChunks - 1))) << 4)) = w[i];
+          } else if (row_valid) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(dst + i * 16) = w[i];
-              }
+            for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(orow + ch * 64 + i * 16) = w[i];
+          }
+        }
+        if (to_peers) {
+          __syncwarp();
+          constexpr int kRowsPerPass = 32 / kRowChunks;  // rows one warp-wide store covers
+          const int c = lane & (kRowChunks - 1);
+#pragma unroll 1
+          for (int pass = 0; pass < 32 / kRowsPerPass; ++pass) {
+            const int rr = pass * kRowsPerPass + lane / kRowChunks;
+            const int Rr = row0 + t * 128 + qd * 32 + rr;
+            const int tqr = Rr >> p.g_shift;
+            if (tqr < qlen) {
+              const uint4 val = *reinterpret_cast<const uint4*>(stage_rows + rr * kRowBytes +
+                                                                ((c ^ (rr & (kRowChunks - 1))) << 4));
+              const int hr = kvh * G + (Rr & (G - 1));
+              const int64_t prow = p.peer.rows ? p.peer.rows[s0 + tqr] : (s0 + tqr);
+              const int64_t off =
+                  (prow * p.peer.stride_t + (int64_t)(p.peer.head_offset + hr) * p.peer.stride_h) * 2 + c * 16;
+              for (int q = 0; q < p.peer.num_peers; ++q)
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.peer.out[q]) + off) = val;
             }
           }
         }

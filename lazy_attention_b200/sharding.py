@@ -17,7 +17,8 @@ is an empty stub, lazy_attn/lazy/engine/core.py:154-156).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Sequence
+import ctypes
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
@@ -141,8 +142,12 @@ class PeerOutput:
     (``la_peer_alloc``), exports it with CUDA IPC (``la_peer_export``) and opens the
     others' (``la_peer_open``); the attention kernels then store each result row straight
     into all of these buffers (``peer_out=`` of the operators), and
-    :meth:`barrier` -- a one-element all-reduce on the current stream -- is all
-    that remains of the collective.  ``head_offset`` is the position of this
+    :meth:`barrier` is all that remains of the collective: one small kernel on the
+    current stream (``la_peer_barrier``) in which every rank announces, with a store
+    into each peer's signal buffer, that its kernels of the step have finished, and
+    waits (bounded) for the others' announcements.  Ranks that share a GPU fall back
+    to a one-element all-reduce: their kernels must not wait on one another on one
+    device.  ``head_offset`` is the position of this
     rank's first head in the full buffers (KV-head sharding); ``rows`` maps local
     output rows to rows of the full buffers (request sharding).
 
@@ -166,35 +171,51 @@ class PeerOutput:
         shape = (rows, heads, head_dim)
         nbytes = rows * heads * head_dim * 2
         self._lib, self._own, self._mapped = lib, None, []
+        self._own_signal, self._signals = None, []
         # Every rank runs the same collectives whatever happens locally, and all
         # ranks fail together if any of them could not export or map a buffer.
         ok, handle = 1, None
-        with torch.cuda.device(device):
+
+        def alloc_and_export(size):
             own = C.c_void_p()
-            if lib.la_peer_alloc(nbytes, C.byref(own)) == 0:
-                self._own = own.value
-                buf = C.create_string_buffer(64)
-                if lib.la_peer_export(self._own, buf) == 0:
-                    handle = buf.raw
-                else:
-                    ok = 0
-            else:
+            if lib.la_peer_alloc(size, C.byref(own)) != 0:
+                return None, None
+            buf = C.create_string_buffer(64)
+            if lib.la_peer_export(own.value, buf) != 0:
+                return own.value, None
+            return own.value, buf.raw
+
+        def open_peer(h):
+            # opened with THIS rank's GPU current: the mapping is made for the GPU whose
+            # kernels will store through it
+            mapped = C.c_void_p()
+            if h is None or lib.la_peer_open(h, C.byref(mapped)) != 0:
+                return None
+            self._mapped.append(mapped.value)
+            return mapped.value
+
+        with torch.cuda.device(device):
+            self._own, handle = alloc_and_export(nbytes)
+            self._own_signal, signal_handle = alloc_and_export(_lib.LA_PEER_SIGNAL_BYTES)
+            if handle is None or signal_handle is None:
                 ok = 0
+            gpu = str(torch.cuda.get_device_properties(device).uuid)
             handles = [None] * self.world
-            dist.all_gather_object(handles, handle, group=group)
+            dist.all_gather_object(handles, (handle, signal_handle, gpu), group=group)
             self.buffers = []
-            for r, h in enumerate(handles):
-                if r == self.rank and self._own is not None:
+            for r, (h, hs, _) in enumerate(handles):
+                if r == self.rank and self._own is not None and self._own_signal is not None:
                     self.buffers.append(_as_tensor(self._own, shape, dtype, device))
+                    self._signals.append(self._own_signal)
                     continue
-                mapped = C.c_void_p()
-                # opened with THIS rank's GPU current: the mapping is made for the GPU whose
-                # kernels will store through it
-                if h is None or lib.la_peer_open(h, C.byref(mapped)) != 0:
+                ptr, sig = open_peer(h), open_peer(hs)
+                if ptr is None or sig is None:
                     ok = 0
                     continue
-                self._mapped.append(mapped.value)
-                self.buffers.append(_as_tensor(mapped.value, shape, dtype, device))
+                self.buffers.append(_as_tensor(ptr, shape, dtype, device))
+                self._signals.append(sig)
+            gpus = [g for (_, _, g) in handles]
+            self._one_rank_per_gpu = len(set(gpus)) == len(gpus)
             torch.cuda.synchronize(device)
         flag = torch.tensor([ok], dtype=torch.int32, device=device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
@@ -220,10 +241,24 @@ class PeerOutput:
         peer.stride_t, peer.stride_h = self.local.stride(0), self.local.stride(1)
         peer.rows = self.rows.data_ptr() if self.rows is not None else None
 
-    def barrier(self) -> None:
-        """All ranks' kernels of the current step have finished (stream-ordered)."""
+    def barrier(self, collective: Optional[bool] = None) -> None:
+        """All ranks' kernels of the current step have finished and their rows have landed
+        (stream-ordered).  ``collective=True`` uses a one-element all-reduce instead of the
+        library's signal kernel (the default only for ranks that share a GPU)."""
         import torch.distributed as dist
-        dist.all_reduce(self._flag, group=self.group)
+        if collective is None:
+            collective = not self._one_rank_per_gpu
+        elif not collective and not self._one_rank_per_gpu:
+            raise RuntimeError("ranks that share a GPU cannot wait for one another inside kernels")
+        if collective:
+            dist.all_reduce(self._flag, group=self.group)
+            return
+        arr = (ctypes.c_void_p * self.world)(*self._signals)
+        stream = torch.cuda.current_stream(self._device).cuda_stream
+        with torch.cuda.device(self._device):
+            if self._lib.la_peer_barrier(arr, self.world, self.rank, stream) != 0:
+                from . import _lib
+                raise RuntimeError(_lib.last_error())
 
     def close(self, collective: bool = True) -> None:
         """Unmaps the peers' buffers, then (after a barrier, so that no peer still has this
@@ -232,12 +267,14 @@ class PeerOutput:
         import torch.distributed as dist
         self.buffers = []
         self.local = None
+        self._signals = []
         for ptr in self._mapped:
             self._lib.la_peer_close(ptr)
         self._mapped = []
         if collective:
             torch.cuda.synchronize()
             dist.barrier(group=self.group)
-        if self._own is not None:
-            self._lib.la_peer_free(self._own)
-            self._own = None
+        for name in ("_own", "_own_signal"):
+            if getattr(self, name) is not None:
+                self._lib.la_peer_free(getattr(self, name))
+                setattr(self, name, None)

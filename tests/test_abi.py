@@ -46,6 +46,11 @@ def test_null_arguments_are_refused_without_a_gpu():
     assert lib.la_decode_fwd(None, None) == _lib.LA_ERR_INVALID_ARGUMENT
     assert lib.la_pack_block_table(None, None, None, None, None, 1, 1, 1, 1, None) == _lib.LA_ERR_INVALID_ARGUMENT
     assert lib.la_build_cos_sin_table(None, 0, 4, 8, 1e4, 0, 1.0, 1.0, 1.0, 8192, None) == _lib.LA_ERR_INVALID_ARGUMENT
+    assert lib.la_peer_barrier(None, 2, 0, None) == _lib.LA_ERR_INVALID_ARGUMENT
+    one = (ctypes.c_void_p * 2)(0x1000, None)
+    assert lib.la_peer_barrier(one, 2, 0, None) == _lib.LA_ERR_INVALID_ARGUMENT   # a rank without a signal buffer
+    assert lib.la_peer_barrier(one, 1, 1, None) == _lib.LA_ERR_INVALID_ARGUMENT   # rank outside the job
+    assert lib.la_peer_barrier(one, _lib.LA_MAX_PEERS + 1, 0, None) == _lib.LA_ERR_INVALID_ARGUMENT
 
 
 def _split_prefill_args():

@@ -5,6 +5,7 @@ boxes with fewer than two GPUs (the sharding logic itself is covered on CPU
 ranks in test_sharding.py)."""
 import os
 import sys
+import time
 
 import pytest
 import torch
@@ -41,13 +42,25 @@ def _worker(rank, world, port, q):
                                      is_lazy=mine["is_lazy"], q_offset=mine["q_offset"], q_mask=mine["q_mask"],
                                      kernel="tensor", peer_out=peer)
             return o
-        want = sharding.gather_head_outputs(run(None), world)
         peer = sharding.PeerOutput(mine["num_tokens"], full["geom"].num_q_heads, g.head_dim, torch.bfloat16, device,
                                    head_offset=rank * g.num_q_heads)
-        run(peer)
-        peer.barrier()
-        torch.cuda.synchronize(device)
-        ok_prefill = bool(torch.equal(peer.local, want))
+        ok_prefill = True
+        # one split: the attention kernel's epilogue stores the rows; three: the merge kernel.
+        # The ranks reach each barrier at different times (host-side delays of different
+        # lengths), and a rank clears its buffer between two barriers, so a barrier that lets
+        # a rank through early shows up as missing rows.
+        for it, splits in enumerate(["1", "3", "1", "3"]):
+            os.environ["LAZY_ATTN_B200_PREFILL_SPLITS"] = splits
+            want = sharding.gather_head_outputs(run(None), world)
+            peer.local.zero_()
+            time.sleep(0.03 * ((rank + it) % world))
+            peer.barrier()
+            run(peer)
+            time.sleep(0.02 * ((rank + it + 1) % world))
+            peer.barrier()
+            torch.cuda.synchronize(device)
+            ok_prefill = ok_prefill and bool(torch.equal(peer.local, want))
+        os.environ.pop("LAZY_ATTN_B200_PREFILL_SPLITS", None)
         # ---- decode sharded by request
         dec = synth.build_decode(synth.GEOM_8B, torch.bfloat16, [[512, 1024], [256], [2048, 160], [512], [1024, 1024]],
                                  seed=22, device=device, kv_dtype="fp8_e4m3", k_scale=0.1, v_scale=0.2)

@@ -57,6 +57,8 @@ def run_cuda(case, op: str, kernel="auto", **kw):
                   k_scale=c["k_scale"], v_scale=c["v_scale"], sm_scale=c["sm_scale"],
                   cos_sin_cache=c["cos_sin_cache"], rotary_dim=c["geom"].head_dim,
                   sliding_window=c.get("sliding_window"), kernel=kernel)
+    if kw.get("peer_out") is not None:
+        common["peer_out"] = kw["peer_out"]
     if op == "lazy_prefill":
         la.context_attention_fwd(c["q"], c["k"], c["v"], out, k_cache=c["k_cache"],
                                  v_cache=c["v_cache"], b_loc=c["block_table"],

@@ -607,7 +607,8 @@ def run_workload(name, args, world, rank, local_rank, device):
     launches = la.launch_count() - launches0
     launches_timed = int(round(launches * steps / (steps + warmup)))
     if launches_per_step is not None:
-        launches_timed = launches_per_step * steps
+        # the graph's kernels, plus the signal kernel that ends a step of the fused gather
+        launches_timed = (launches_per_step + int(peers is not None and args.barrier == "signal")) * steps
     ms_per_step = total_ms / steps
     value = tokens_all / (ms_per_step * 1e-3)
     assert abs(value * ms_per_step * 1e-3 - tokens_all) < 1.0

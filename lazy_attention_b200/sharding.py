@@ -168,10 +168,12 @@ class PeerOutput:
         if self.world > 8:
             raise ValueError("at most 8 ranks")
         device = torch.device(device)
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
         shape = (rows, heads, head_dim)
         nbytes = rows * heads * head_dim * 2
         self._lib, self._own, self._mapped = lib, None, []
-        self._own_signal, self._signals = None, []
+        self._own_signal, self._signals, self._signal_array = None, [], None
         # Every rank runs the same collectives whatever happens locally, and all
         # ranks fail together if any of them could not export or map a buffer.
         ok, handle = 1, None
@@ -253,12 +255,17 @@ class PeerOutput:
         if collective:
             dist.all_reduce(self._flag, group=self.group)
             return
-        arr = (ctypes.c_void_p * self.world)(*self._signals)
+        if self._signal_array is None:
+            self._signal_array = (ctypes.c_void_p * self.world)(*self._signals)
         stream = torch.cuda.current_stream(self._device).cuda_stream
-        with torch.cuda.device(self._device):
-            if self._lib.la_peer_barrier(arr, self.world, self.rank, stream) != 0:
-                from . import _lib
-                raise RuntimeError(_lib.last_error())
+        if torch.cuda.current_device() == self._device.index:
+            code = self._lib.la_peer_barrier(self._signal_array, self.world, self.rank, stream)
+        else:
+            with torch.cuda.device(self._device):
+                code = self._lib.la_peer_barrier(self._signal_array, self.world, self.rank, stream)
+        if code != 0:
+            from . import _lib
+            raise RuntimeError(_lib.last_error())
 
     def close(self, collective: bool = True) -> None:
         """Unmaps the peers' buffers, then (after a barrier, so that no peer still has this
@@ -267,7 +274,7 @@ class PeerOutput:
         import torch.distributed as dist
         self.buffers = []
         self.local = None
-        self._signals = []
+        self._signals, self._signal_array = [], None
         for ptr in self._mapped:
             self._lib.la_peer_close(ptr)
         self._mapped = []

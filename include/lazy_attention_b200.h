@@ -351,8 +351,9 @@ int la_write_paged_cache(const LaWriteCacheArgs* args, void* stream);
  *                   call it the same number of times (the round counter lives in the buffer, so a
  *                   captured launch can be replayed).  One process per GPU: ranks that share a GPU
  *                   must not use it (their kernels would wait on one another on one device).  The
- *                   wait is bounded (about 4 s of GPU clock); a rank that never arrives leaves
- *                   LA_ERR_DEVICE_STATUS for la_device_status() and the kernel returns.
+ *                   wait is bounded (about 10 s of GPU clock; LAZY_ATTN_B200_BARRIER_LIMIT_MS in the
+ *                   environment overrides it); a rank that never arrives leaves the code 300 + its
+ *                   number for la_device_status() / la_check_device() and the kernel returns.
  */
 #define LA_IPC_HANDLE_BYTES 64
 #define LA_PEER_SIGNAL_BYTES 256

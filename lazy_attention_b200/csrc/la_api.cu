@@ -289,12 +289,12 @@ extern "C" int la_peer_close(void* mapped) {
 namespace la {
 namespace {
 constexpr int kRoundWord = 32;
-constexpr uint64_t kBarrierLimitNs = 4000ull * 1000 * 1000;
+constexpr uint64_t kBarrierLimitNs = 10000ull * 1000 * 1000;  // ranks are processes: allow for host-side skew
 struct PeerSignals {
   uint32_t* ptr[LA_MAX_PEERS];
 };
 
-__global__ void peer_barrier_kernel(PeerSignals s, int world, int rank, int* status) {
+__global__ void peer_barrier_kernel(PeerSignals s, int world, int rank, uint64_t limit_ns, int* status) {
   const int lane = threadIdx.x;
   uint32_t* mine = s.ptr[rank];
   const uint32_t round = *reinterpret_cast<volatile uint32_t*>(mine + kRoundWord) + 1u;
@@ -317,7 +317,7 @@ __global__ void peer_barrier_kernel(PeerSignals s, int world, int rank, int* sta
     if ((++polls & 63u) == 0) {
       const uint64_t now = sm100::global_timer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kBarrierLimitNs) {
+      if (now - t0 > limit_ns) {
         if (status) atomicCAS(status, 0, 300 + lane);  // rank `lane` never arrived
         break;
       }
@@ -338,7 +338,12 @@ extern "C" int la_peer_barrier(void* const* signals, int32_t world, int32_t rank
                "la_peer_barrier: signal buffer of rank %d is null or unaligned", r);
     s.ptr[r] = reinterpret_cast<uint32_t*>(signals[r]);
   }
-  la::peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(s, world, rank, la::device_status_ptr());
+  uint64_t limit_ns = la::kBarrierLimitNs;
+  if (const char* e = getenv("LAZY_ATTN_B200_BARRIER_LIMIT_MS")) {  // tests of the expiry path
+    const long ms = atol(e);
+    if (ms >= 1 && ms <= 60000) limit_ns = (uint64_t)ms * 1000000ull;
+  }
+  la::peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(s, world, rank, limit_ns, la::device_status_ptr());
   LA_CHECK_CUDA(cudaGetLastError());
   la::count_launch();
   return LA_OK;

@@ -106,3 +106,31 @@ def test_signal_kernel_one_rank():
         assert int(words.abs().sum()) == 6, "only the rank's own slot and the round counter are written"
     finally:
         lib.la_peer_free(sig)
+
+
+def test_signal_kernel_gives_up_on_a_rank_that_never_arrives(monkeypatch):
+    """Rank 0 of 2 with a second signal buffer nobody writes: the wait runs out after the (shortened)
+    limit, the kernel returns, the status word names the missing rank, and the device stays usable."""
+    monkeypatch.setenv("LAZY_ATTN_B200_BARRIER_LIMIT_MS", "200")
+    lib = _lib.load()
+    mine, silent = C.c_void_p(), C.c_void_p()
+    assert lib.la_peer_alloc(_lib.LA_PEER_SIGNAL_BYTES, C.byref(mine)) == 0, _lib.last_error()
+    assert lib.la_peer_alloc(_lib.LA_PEER_SIGNAL_BYTES, C.byref(silent)) == 0, _lib.last_error()
+    try:
+        assert la.device_status() == 0
+        arr = (C.c_void_p * 2)(mine.value, silent.value)
+        assert lib.la_peer_barrier(arr, 2, 0, torch.cuda.current_stream().cuda_stream) == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        assert lib.la_check_device() == _lib.LA_ERR_DEVICE_STATUS
+        assert "301" in _lib.last_error()
+        assert la.device_status() == 0, "reading the status clears it"
+        # the context is intact: a one-rank round still completes
+        one = (C.c_void_p * 1)(mine.value)
+        assert lib.la_peer_barrier(one, 1, 0, torch.cuda.current_stream().cuda_stream) == 0
+        torch.cuda.synchronize()
+        assert la.device_status() == 0
+        x = torch.arange(8, device="cuda")
+        assert int(x.sum()) == 28
+    finally:
+        lib.la_peer_free(mine)
+        lib.la_peer_free(silent)

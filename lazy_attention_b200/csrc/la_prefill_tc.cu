@@ -43,9 +43,22 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kThreadsTc = 14 * 32;
 constexpr int kSoftmaxThreads = 8 * 32;
 constexpr int kWarpStage = 8, kWarpMma = 12;  // first staging warp, MMA-issue warp (the TMA warp follows)
+// Per-role register budgets (setmaxnreg works on whole warpgroups, so the CTA is padded to 16
+// warps; warps 14 and 15 only take part in the budget change and the final barriers).  A raise
+// can only take registers the CTA's other warpgroups have released: the budgets must add up to
+// at most threads x launch registers, else the raise waits forever.
+constexpr int kThreadsTc = 16 * 32;
+constexpr int kLaunchRegs = 128;                       // what ptxas reports for 512 threads, one CTA per SM
+// Measured on the 65536-token prefill workload (same box, ms per call): no budgets (14 warps x 128) 4.19-4.25,
+// 168/112/64 4.19, 176/104/56 4.07-4.10, 184/96/48 4.09-4.12.
+constexpr int kRegsSoftmax = 176, kRegsStage = 104, kRegsIssue = 56;
+static_assert(kSoftmaxThreads * kRegsSoftmax + 128 * kRegsStage + 128 * kRegsIssue <= kThreadsTc * kLaunchRegs,
+              "register budgets exceed what the CTA is launched with");
+static_assert(kRegsSoftmax % 8 == 0 && kRegsStage % 8 == 0 && kRegsIssue % 8 == 0, "budgets are multiples of 8");
+template <int N> __device__ __forceinline__ void regs_raise() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void regs_lower() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 constexpr int kRowsPerCta = 256;
 constexpr int kTileN = 128;
 constexpr int kPagesPerTile = 8;
@@ -488,6 +501,7 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
 
   if (warp < kWarpStage) {
     // =============================== softmax ===============================
+    regs_raise<kRegsSoftmax>();
     // One thread per score row.  The row's 128 scores of a tile are consumed in four
     // 32-column chunks: while one chunk is scaled, exponentiated and packed, the
     // tensor-memory load of the next is already in flight.  P (two keys per column) is
@@ -877,6 +891,7 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
     }
   } else if (warp < kWarpMma) {
     // =============================== operand staging ===============================
+    regs_lower<kRegsStage>();
     const int i = tid - kWarpStage * 32;  // 0..127
     bool ok = true;
     const uint8_t* cs = reinterpret_cast<const uint8_t*>(p.cs);
@@ -1240,6 +1255,7 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
     }
   } else if (warp == kWarpMma) {
     // =============================== MMA issue ===============================
+    regs_lower<kRegsIssue>();
     // In a pair only the first CTA issues: each MMA covers the 128 rows of a row tile in both
     // CTAs (M = 256), reading Q and P from each CTA and half of K / V from each CTA.
     if (ntiles > 0 && cta_rank == 0) {
@@ -1333,8 +1349,11 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
       if (ok && issuer) commit(&bar_o_done);
       __syncwarp();
       }
+  } else if (warp > kWarpMma + 1) {
+    regs_lower<kRegsIssue>();  // padding warps of the last warpgroup
   } else {
     // =============================== TMA issue ===============================
+    regs_lower<kRegsIssue>();
     bool ok = true;
     const int j_end = KVF8 != 0 ? j0 : min(j1, n_ctx);  // fp8 caches are staged with plain loads
     for (int j = j0; j < j_end && ok; ++j) {
@@ -1630,6 +1649,17 @@ size_t tc_prefill_workspace_bytes(const LaPrefillArgs& a) { return make_plan(a).
 
 namespace {
 
+// The per-role register budgets assume the registers per thread the kernel is launched with; a build
+// that came out with fewer would leave the softmax warps waiting for registers nobody can release.
+int check_launch_registers(const void* kern) {
+  cudaFuncAttributes attr;
+  LA_CHECK_CUDA(cudaFuncGetAttributes(&attr, kern));
+  LA_REQUIRE(attr.numRegs == kLaunchRegs, LA_ERR_UNSUPPORTED,
+             "prefill kernel was built with %d registers per thread, its register budgets need %d", attr.numRegs,
+             kLaunchRegs);
+  return LA_OK;
+}
+
 template <int D, bool BF16, int KVF8>
 int launch_tc_kv(const LaPrefillArgs& a, const TcParams& p, const MapPair& mp, const TcPlan& pl,
                   cudaStream_t stream) {
@@ -1641,6 +1671,7 @@ int launch_tc_kv(const LaPrefillArgs& a, const TcParams& p, const MapPair& mp, c
   LA_CHECK_CUDA(cudaGetDevice(&dev));
   if (((prepared.load(std::memory_order_acquire) >> (dev & 63)) & 1ull) == 0) {
     LA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    if (const int rc = check_launch_registers(reinterpret_cast<const void*>(kern)); rc != LA_OK) return rc;
     prepared.fetch_or(1ull << (dev & 63), std::memory_order_release);
   }
   dim3 grid(pl.mblocks, a.num_kv_heads, a.batch * pl.n_splits);
@@ -1667,6 +1698,7 @@ int launch_tc_pair(const LaPrefillArgs& a, const TcParams& p, const MapPair& mp,
   LA_CHECK_CUDA(cudaGetDevice(&dev));
   if (((prepared.load(std::memory_order_acquire) >> (dev & 63)) & 1ull) == 0) {
     LA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    if (const int rc = check_launch_registers(reinterpret_cast<const void*>(kern)); rc != LA_OK) return rc;
     prepared.fetch_or(1ull << (dev & 63), std::memory_order_release);
   }
   dim3 grid(pl.mblocks, a.num_kv_heads, a.batch * pl.n_splits);  // x is even: clusters of (2, 1, 1)

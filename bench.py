@@ -616,7 +616,7 @@ def run_workload(name, args, world, rank, local_rank, device):
     # ---- kernel-only time of this rank's attention call (roofline), replayed and eager ---------
     _, kper = time_steps(fast_step, steps, 1, device, 1, flush)
     kern_ms = sum(kper) / len(kper)
-    _, eper = time_steps(eager_step, steps, 2, device, 1, flush)
+    _, eper = time_steps(eager_step, steps, warmup, device, 1, flush)
     eager_ms = sum(eper) / len(eper)
     pk = peaks()
     traffic = None

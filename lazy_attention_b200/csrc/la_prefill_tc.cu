@@ -390,7 +390,6 @@ struct TcCfg {
 
 template <int D, bool BF16, int KVF8, bool PAIR>
 __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const CUtensorMap& mapV, const TcParams& p) {
-  static_assert(!PAIR || KVF8 == 0, "CTA pairs are implemented for 16-bit caches");
   using Cfg = TcCfg<D, PAIR>;
   constexpr int KS = Cfg::kStages;
   constexpr int NCH = D / 8;  // 16-byte chunks per row
@@ -908,6 +907,27 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
       if (jn < j1 && jn < n_ctx) {
         const int stn = (jn - j0) % KS, un = (jn - j0) / KS;
         if (un > 0) good = mbar_wait(&bar_k_empty[stn], (uint32_t)(un - 1) & 1u, p.status, 204);
+        if constexpr (PAIR) {
+          // This CTA's 64 keys, two threads per key.  Thread `hc` of a key converts the raw pieces
+          // g in [hc * NL/4, (hc+1) * NL/4) and their rotation partners g + NL/2; their raw bytes
+          // land in the first NL/2 of the chunk slots that this thread alone writes later.
+          constexpr int NL = D / 16;
+          const int key = i & 63, hc = i >> 6;
+          const int page = jn * kPagesPerTile + 4 * (int)cta_rank + (key >> 4);
+          if (good && page < ctx_pages) {
+            int64_t blk = page_block(page);
+            if (blk < 0 || blk >= p.num_blocks) blk = 0;
+            const uint8_t* src = p.kc + blk * p.kc_sb + (int64_t)kvh * p.kc_sh + (key & 15) * 16;
+            const uint32_t dst =
+                smem_u32(sK + stn * Cfg::kKStageBytes + (key >> 3) * Cfg::kRowGroupBytes + (key & 7) * 16);
+#pragma unroll
+            for (int q = 0; q < NL / 4; ++q) {
+              const int g = hc * (NL / 4) + q;
+              cp_async_16(dst + (hc * (NL / 2) + q) * 128, src + g * 256);
+              cp_async_16(dst + (hc * (NL / 2) + NL / 4 + q) * 128, src + (g + NL / 2) * 256);
+            }
+          }
+        } else {
         const int page = jn * kPagesPerTile + (i >> 4);
         if (good && page < ctx_pages) {
           int64_t blk = page_block(page);
@@ -916,6 +936,7 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
           const uint32_t dst = smem_u32(sK + stn * Cfg::kTileBytes + (i >> 3) * Cfg::kRowGroupBytes + (i & 7) * 16);
 #pragma unroll
           for (int g = 0; g < D / 16; ++g) cp_async_16(dst + g * 128, src + g * 256);
+        }
         }
       }
       cp_async_commit();
@@ -928,6 +949,20 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
         if (un > 0) good = mbar_wait(&bar_v_empty[stn], (uint32_t)(un - 1) & 1u, p.status, 205);
         const int npages = min(kPagesPerTile, ctx_pages - jn * kPagesPerTile);
         if (good) {
+          if constexpr (PAIR) {
+            // this CTA's half of the head dimension of every page: D/2 rows of 16 tokens per page
+#pragma unroll
+            for (int it = 0; it < D / 32; ++it) {
+              const int idx = i + it * 128;
+              const int pg = idx / (D / 2), dl = idx - pg * (D / 2);
+              if (pg < npages) {
+                int64_t vb = page_block(jn * kPagesPerTile + pg);
+                if (vb < 0 || vb >= p.num_blocks) vb = 0;
+                cp_async_16(smem_u32(sV + stn * Cfg::kVStageBytes + pg * Cfg::kVPageBytes + (dl >> 3) * 256 + (dl & 7) * 16),
+                            p.vc + vb * p.vc_sb + (int64_t)kvh * p.vc_sh + ((int)cta_rank * (D / 2) + dl) * 16);
+              }
+            }
+          } else {
 #pragma unroll
           for (int it = 0; it < D / 16; ++it) {  // one (page, dim) row of 16 tokens per piece
             const int idx = i + it * 128;
@@ -938,6 +973,7 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
               cp_async_16(smem_u32(sV + stn * Cfg::kTileBytes + pg * Cfg::kPageBytes + (d >> 3) * 256 + (d & 7) * 16),
                           p.vc + vb * p.vc_sb + (int64_t)kvh * p.vc_sh + d * 16);
             }
+          }
           }
         }
       }
@@ -979,6 +1015,62 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
             if (pos >= p.cs_rows) pos = (int)p.cs_rows - 1;
           }
           const uint8_t* crow = cs + (int64_t)pos * D * 2;
+          if constexpr (KVF8 != 0) {
+            // fp8 cache: this CTA's raw pages of the tile were copied (cp.async, one tile ahead)
+            // into the operand stage itself, every 16-byte piece into a chunk slot that only its
+            // own thread reads and later overwrites.  Convert to f16 (exact), rotate K, and
+            // write the MMA layouts in place.
+            constexpr int NL = D / 16;
+            const bool present = page < ctx_pages;
+            const int npages = min(kPagesPerTile, ctx_pages - j * kPagesPerTile);
+            cp_async_wait_group<1>();  // K pieces of tile j have landed
+            uint4 kraw[NL / 2];
+#pragma unroll
+            for (int q = 0; q < NL / 2; ++q)
+              kraw[q] = present ? *reinterpret_cast<const uint4*>(rowp + (hc * (NL / 2) + q) * 128)
+                                : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int q = 0; q < NL / 4; ++q) {  // dims [16g, 16g+16) and their partners at +D/2
+              const int g = hc * (NL / 4) + q;
+              uint4 a0, a1, b0, b1;
+              fp8x16_to_f16<KVF8>(kraw[q], a0, a1);
+              fp8x16_to_f16<KVF8>(kraw[NL / 4 + q], b0, b1);
+              if (pos > 0) {
+                const uint4 c0 = __ldg(reinterpret_cast<const uint4*>(crow + g * 32));
+                const uint4 c1 = __ldg(reinterpret_cast<const uint4*>(crow + g * 32 + 16));
+                const uint4 s0v = __ldg(reinterpret_cast<const uint4*>(crow + D + g * 32));
+                const uint4 s1v = __ldg(reinterpret_cast<const uint4*>(crow + D + g * 32 + 16));
+                rotate_chunk_f16<BF16>(a0, b0, c0, s0v);
+                rotate_chunk_f16<BF16>(a1, b1, c1, s1v);
+              }
+              *reinterpret_cast<uint4*>(rowp + (2 * g) * 128) = a0;
+              *reinterpret_cast<uint4*>(rowp + (2 * g + 1) * 128) = a1;
+              *reinterpret_cast<uint4*>(rowp + (2 * g + NCH / 2) * 128) = b0;
+              *reinterpret_cast<uint4*>(rowp + (2 * g + 1 + NCH / 2) * 128) = b1;
+            }
+            fence_proxy_async_smem();
+            arrive_at_leader(&bar_k_ready[st]);
+            ok = issue_raw_k(j + 1);
+            if (!ok) break;
+            cp_async_wait_group<1>();  // V pieces of tile j have landed
+#pragma unroll
+            for (int it = 0; it < D / 32; ++it) {
+              const int idx = i + it * 128;
+              const int pg = idx / (D / 2), dl = idx - pg * (D / 2);
+              if (pg < npages) {
+                uint8_t* dst = vst + pg * Cfg::kVPageBytes + (dl >> 3) * 256 + (dl & 7) * 16;
+                const uint4 raw = *reinterpret_cast<const uint4*>(dst);
+                uint4 lo, hi;
+                fp8x16_to_f16<KVF8>(raw, lo, hi);
+                *reinterpret_cast<uint4*>(dst) = lo;
+                *reinterpret_cast<uint4*>(dst + 128) = hi;
+              }
+            }
+            fence_proxy_async_smem();
+            arrive_at_leader(&bar_v_ready[st]);
+            ok = issue_raw_v(j + 1);
+            continue;
+          }
           uint4 cv[NP], sv[NP];
           if (pos > 0) {
 #pragma unroll
@@ -1034,6 +1126,10 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
                   const uint4 svv = __ldg(reinterpret_cast<const uint4*>(crow + D + (g0 + g) * 16));
                   rotate_chunk<BF16>(a, bq, cvv, svv);
                 }
+                if constexpr (BF16 && !MB) {
+                  a = bf16x8_to_f16x8(a);
+                  bq = bf16x8_to_f16x8(bq);
+                }
               }
               *reinterpret_cast<uint4*>(rowp + (g0 + g) * 128) = a;
               *reinterpret_cast<uint4*>(rowp + (g0 + g + NCH / 2) * 128) = bq;
@@ -1060,6 +1156,7 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
                   if (slot >= 0)
                     cache_put_v<BF16, KVF8>(p, slot >> 4, (int)(slot & 15), kvh, (int)cta_rank * (D / 2) + g * 8, val, put_vs);
                 }
+                if constexpr (KVF8 != 0) val = to_f16x8_scaled<BF16>(val, 1.f / out_scale);
               }
               const uint16_t* e = reinterpret_cast<const uint16_t*>(&val);
 #pragma unroll
@@ -1417,10 +1514,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
 
 // The same kernel run by clusters of two CTAs (consecutive row blocks of one request and KV
 // head), 16-bit caches only.  mapV copies half of the head dimension of a page.
-template <int D, bool BF16>
+template <int D, bool BF16, int KVF8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsTc, 1)
 prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, TcParams p) {
-  prefill_tc_body<D, BF16, 0, true>(mapK, mapV, p);
+  prefill_tc_body<D, BF16, KVF8, true>(mapK, mapV, p);
 }
 
 // Merge the per-split partial results: out = sum_s 2^(m_s - m*) O_s / sum_s 2^(m_s - m*) l_s.
@@ -1571,12 +1668,12 @@ TcPlan make_plan(const LaPrefillArgs& a) {
   const int G = a.num_q_heads / a.num_kv_heads;
   TcPlan pl;
   pl.mblocks = (int)(((int64_t)a.max_query_len * G + kRowsPerCta - 1) / kRowsPerCta);
-  // CTA pairs: 16-bit caches, and at least two row blocks per (request, KV head) so that a
-  // pair is not half empty by construction.
-  pl.pair = a.kv_dtype == a.q_dtype && pl.mblocks >= 2;
+  // CTA pairs: at least two row blocks per (request, KV head), so that a pair is not half
+  // empty by construction.
+  pl.pair = pl.mblocks >= 2;
   if (const char* e = getenv("LAZY_ATTN_B200_PREFILL_PAIR")) {  // experiments only
     if (e[0] == '0') pl.pair = false;
-    if (e[0] == '1' && a.kv_dtype == a.q_dtype) pl.pair = true;
+    if (e[0] == '1') pl.pair = true;
   }
   if (pl.pair) pl.mblocks = (pl.mblocks + 1) & ~1;
   pl.rows_cap = (int64_t)pl.mblocks * kRowsPerCta;
@@ -1688,11 +1785,11 @@ int launch_tc_kv(const LaPrefillArgs& a, const TcParams& p, const MapPair& mp, c
   return LA_OK;
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, int KVF8>
 int launch_tc_pair(const LaPrefillArgs& a, const TcParams& p, const MapPair& mp, const TcPlan& pl,
                    cudaStream_t stream) {
   using Cfg = TcCfg<D, true>;
-  auto kern = prefill_tc_pair_kernel<D, BF16>;
+  auto kern = prefill_tc_pair_kernel<D, BF16, KVF8>;
   static std::atomic<uint64_t> prepared{0};
   int dev = 0;
   LA_CHECK_CUDA(cudaGetDevice(&dev));
@@ -1717,7 +1814,11 @@ int launch_tc_pair(const LaPrefillArgs& a, const TcParams& p, const MapPair& mp,
 
 template <int D, bool BF16>
 int launch_tc(const LaPrefillArgs& a, const TcParams& p, const MapPair& mp, const TcPlan& pl, cudaStream_t stream) {
-  if (pl.pair) return launch_tc_pair<D, BF16>(a, p, mp, pl, stream);
+  if (pl.pair) {
+    if (a.kv_dtype == LA_DTYPE_FP8_E4M3) return launch_tc_pair<D, BF16, 1>(a, p, mp, pl, stream);
+    if (a.kv_dtype == LA_DTYPE_FP8_E5M2) return launch_tc_pair<D, BF16, 2>(a, p, mp, pl, stream);
+    return launch_tc_pair<D, BF16, 0>(a, p, mp, pl, stream);
+  }
   if (a.kv_dtype == LA_DTYPE_FP8_E4M3) return launch_tc_kv<D, BF16, 1>(a, p, mp, pl, stream);
   if (a.kv_dtype == LA_DTYPE_FP8_E5M2) return launch_tc_kv<D, BF16, 2>(a, p, mp, pl, stream);
   return launch_tc_kv<D, BF16, 0>(a, p, mp, pl, stream);

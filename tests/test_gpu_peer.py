@@ -70,7 +70,7 @@ def test_prefill_gather_rows(splits, geom, dtype, monkeypatch):
 
 
 def test_prefill_gather_rows_fp8_cache(monkeypatch):
-    """The single-CTA kernel (fp8 caches) shares the epilogue."""
+    """fp8 caches (pages converted in shared memory by the staging warps) share the epilogue."""
     monkeypatch.setenv("LAZY_ATTN_B200_PREFILL_SPLITS", "1")
     reqs = [dict(docs=[2, 0, 1], qlen=200), dict(docs=[3, 6], qlen=257)]
     case = synth.build_prefill(synth.GEOM_8B, torch.bfloat16, POOL, reqs, seed=32, variant="lazy", device="cuda",

@@ -1513,7 +1513,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
 }
 
 // The same kernel run by clusters of two CTAs (consecutive row blocks of one request and KV
-// head), 16-bit caches only.  mapV copies half of the head dimension of a page.
+// head).  mapV copies half of the head dimension of a page (16-bit caches; fp8 pages are copied by the staging warps).
 template <int D, bool BF16, int KVF8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsTc, 1)
 prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, TcParams p) {

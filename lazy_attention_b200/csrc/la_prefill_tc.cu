@@ -34,6 +34,7 @@
 #include <unordered_map>
 
 #include <atomic>
+#include <type_traits>
 
 #include "la_common.cuh"
 #include "la_sm100.cuh"
@@ -588,22 +589,14 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
       }
       return v;
     };
-    // One 32-column chunk: mask, row maximum, lazy rescale, exponentials, P.
-    auto do_chunk = [&](uint32_t (&sc)[32], const int c, const int j, const bool self, const bool tile_full,
-                        const int vc, const int n0, const float scale_log2) {
-      const int col0 = c * 32;
-      if (self) {
-        const int lim = tq - (n0 + col0);  // columns 0..lim are visible
+    // One 32-column chunk of a new-token tile: causal mask, row maximum, lazy rescale,
+    // exponentials, P.
+    auto do_chunk = [&](uint32_t (&sc)[32], const int c, const int j, const int n0, const float scale_log2) {
+      {
+        const int lim = tq - (n0 + c * 32);  // columns 0..lim are visible
 #pragma unroll
         for (int i = 0; i < 32; ++i)
           if (i > lim) sc[i] = 0xff800000u;
-      } else if (!tile_full) {
-        const int va = __shfl_sync(0xffffffffu, vc, 2 * c), vb = __shfl_sync(0xffffffffu, vc, 2 * c + 1);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          if (i >= va) sc[i] = 0xff800000u;
-          if (i >= vb) sc[16 + i] = 0xff800000u;
-        }
       }
       float mx0 = fmax3(__uint_as_float(sc[0]), __uint_as_float(sc[1]), __uint_as_float(sc[2]));
       float mx1 = fmax3(__uint_as_float(sc[3]), __uint_as_float(sc[4]), __uint_as_float(sc[5]));
@@ -693,19 +686,39 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
       tc_fence_after_sync();
       LA_STAMP(t * 8 + 0, j - j0);
       uint32_t sa[32], sb[32];
-      if (tile_full) {
-        // ---- fast path (every key of the tile is visible): two passes over the row.
+      // Cached tiles: two passes over the row, compiled twice.  RAGGED: keys that do not exist
+      // (the padding at the end of a document's last page, the slots past the context in its last
+      // page) are set to -inf right after each load, by the per-page counts in `vc`; the copy
+      // for full tiles carries no trace of it.  (One copy with run-time tests cost the full tiles
+      // 3-5 %, this form 1.3 %, and ragged tiles on the chunk-by-chunk path cost a workload of
+      // ragged documents 4 %.)
+      auto two_pass = [&](auto ragged_tag) {
+        constexpr bool RAGGED = decltype(ragged_tag)::value;
+        auto mask_chunk = [&](uint32_t (&sc)[32], const int c) {
+          if constexpr (RAGGED) {
+            const int va = __shfl_sync(0xffffffffu, vc, 2 * c), vb = __shfl_sync(0xffffffffu, vc, 2 * c + 1);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              if (i >= va) sc[i] = 0xff800000u;
+              if (i >= vb) sc[16 + i] = 0xff800000u;
+            }
+          }
+        };
         // Pass A: the row maximum of the whole tile, so that the one decision about the
         // running maximum is taken before any exponential is formed.
         tmem_ld32(tS, sa);
         tmem_ld32(tS + 32, sb);
         tmem_ld_wait_for(sa);
         tie_after_wait(sb);
+        mask_chunk(sa, 0);
+        mask_chunk(sb, 1);
         float mx_a = row_max32(sa), mx_b = row_max32(sb);
         tmem_ld32(tS + 64, sa);
         tmem_ld32(tS + 96, sb);
         tmem_ld_wait_for(sa);
         tie_after_wait(sb);
+        mask_chunk(sa, 2);
+        mask_chunk(sb, 3);
         mx_a = fmaxf(mx_a, row_max32(sa));
         mx_b = fmaxf(mx_b, row_max32(sb));
         const float m_tile = fmaxf(mx_a, mx_b) * scale_log2;
@@ -766,9 +779,11 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
         tmem_ld_wait_for(sa);
         tmem_ld32(tS + 32, sb);
         LA_STAMP(t * 8 + 3, j - j0);
+        mask_chunk(sa, 0);
         exp_chunk(sa, 0);
         tmem_ld_wait_for(sb);
         LA_STAMP(t * 8 + 4, j - j0);
+        mask_chunk(sb, 1);
         exp_chunk(sb, 1);
         LA_STAMP(t * 8 + 5, j - j0);
         l_sum = fmaf((acc_a.x + acc_a.y) + (acc_b.x + acc_b.y), kUnbias, l_sum);
@@ -776,25 +791,32 @@ __device__ __forceinline__ void prefill_tc_body(const CUtensorMap& mapK, const C
         tc_fence_before_sync();
         arrive_at_leader(&bar_p_full[t]);
         LA_STAMP(t * 8 + 6, j - j0);
+      };
+      if (tile_full) {
+        two_pass(std::false_type{});
         continue;
       }
-      // ---- tiles with masked keys (ragged pages, causal new-token tiles): chunk by chunk
+      if (!self) {
+        two_pass(std::true_type{});
+        continue;
+      }
+      // ---- new-token tiles (causal mask per row): chunk by chunk
       tmem_ld32(tS, sa);
       tmem_ld_wait();
       LA_STAMP(t * 8 + 1, j - j0);
       tmem_ld32(tS + 32, sb);
-      do_chunk(sa, 0, j, self, tile_full, vc, n0, scale_log2);
+      do_chunk(sa, 0, j, n0, scale_log2);
       LA_STAMP(t * 8 + 2, j - j0);
       tmem_ld_wait();
       tmem_ld32(tS + 64, sa);
-      do_chunk(sb, 1, j, self, tile_full, vc, n0, scale_log2);
+      do_chunk(sb, 1, j, n0, scale_log2);
       LA_STAMP(t * 8 + 3, j - j0);
       tmem_ld_wait();
       tmem_ld32(tS + 96, sb);
       tmem_ld_wait();  // P of chunk 2 goes over the columns of chunk 3: have chunk 3 in registers first
-      do_chunk(sa, 2, j, self, tile_full, vc, n0, scale_log2);
+      do_chunk(sa, 2, j, n0, scale_log2);
       LA_STAMP(t * 8 + 4, j - j0);
-      do_chunk(sb, 3, j, self, tile_full, vc, n0, scale_log2);
+      do_chunk(sb, 3, j, n0, scale_log2);
       LA_STAMP(t * 8 + 5, j - j0);
       tmem_st_wait();
       tc_fence_before_sync();

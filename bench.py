@@ -36,7 +36,9 @@ back, every step - measured in sequence on one stream and as a three-stream
 pipeline over two buffer sets, the better of the two reported; at N > 1 every
 rank uploads its own shard and reads back its 1/N slice of the gathered rows,
 so the job reads the result back once.  Timing is CUDA events on the launching
-stream, max over ranks.
+stream, max over ranks.  ``speedup_vs_ideal`` is the time the whole job's
+algorithmic work, spread evenly over the N ranks, would take at the measured peak,
+divided by rank 0's kernel time (at N = 1 it equals ``roofline.frac``).
 
 ``--impl reference`` times the CPU oracle (a float32 torch restatement of the
 reference kernels) with all host threads; each step is one call over a bounded
@@ -637,6 +639,14 @@ def run_workload(name, args, world, rank, local_rank, device):
                     kernel_ms=kern_ms, algorithmic_flops=flops, algorithmic_bytes=byts)
     if world > 1:
         roof["scope"] = "rank 0's shard: its kernel time against its share of the work"
+    # the whole job's work, spread evenly over the ranks, at the peak, against rank 0's kernel time
+    work = torch.tensor([flops, byts], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(work)
+    ideal_ms = (float(work[0]) / world / (roof["peak"] * 1e12) if roof["bound"] == "tensor"
+                else float(work[1]) / world / (roof["peak"] * 1e9)) * 1e3
+    roof["ideal_ms_per_rank_at_peak"] = ideal_ms
+    speedup_vs_ideal = ideal_ms / kern_ms
 
     # ---- end to end through the public API with host buffers ----------------------------
     e2e = None
@@ -742,7 +752,8 @@ def run_workload(name, args, world, rank, local_rank, device):
                            partition=info["partition"], l2=info["l2"]),
                execution=dict(launch=launch_mode, gather=gather_mode, eager_ms_per_step=eager_ms,
                               replay_ms_per_step=kern_ms),
-               roofline=roof, e2e=e2e, gpu_launches=launches_timed, clocks=clk.summary())
+               roofline=roof, speedup_vs_ideal=speedup_vs_ideal, e2e=e2e, gpu_launches=launches_timed,
+               clocks=clk.summary())
     if gather_check is not None:
         res["gather_check"] = gather_check
     if world == 1 and not args.no_triton and args.scale == 1.0 and args.shard_of == 1:
@@ -784,7 +795,7 @@ def main():
             r = run_workload(name, args, world, rank, local_rank, device)
             torch.cuda.empty_cache()
             also[name] = {k: r[k] for k in ("value", "unit", "ms_per_step", "tokens_per_step", "dtype", "config",
-                                            "execution", "roofline", "e2e", "gpu_launches", "gather_check",
+                                            "execution", "roofline", "speedup_vs_ideal", "e2e", "gpu_launches", "gather_check",
                                             "triton_baseline", "speedup_vs_triton") if k in r}
 
     if rank == 0:
@@ -792,7 +803,7 @@ def main():
                     warmup=args.warmup, ms_per_step=head["ms_per_step"], higher_is_better=True,
                     scaling=head["scaling"], vs_baseline=None, dtype=head["dtype"], data="synthetic",
                     tokens_per_step=head["tokens_per_step"], config=head["config"], execution=head["execution"],
-                    roofline=head["roofline"], e2e=head["e2e"],
+                    roofline=head["roofline"], speedup_vs_ideal=head["speedup_vs_ideal"], e2e=head["e2e"],
                     gpu_launches=head["gpu_launches"] + sum(a["gpu_launches"] for a in also.values()),
                     clocks=head["clocks"])
         for k in ("gather_check", "triton_baseline", "speedup_vs_triton"):

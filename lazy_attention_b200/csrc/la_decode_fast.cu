@@ -181,6 +181,20 @@ __device__ __forceinline__ float rope_inv_freq(const DecParams& p, int i) {
   return (1.f - smooth) * inv / p.rope_factor + smooth * inv;
 }
 
+// cos / sin of position x inverse frequency for dims d0 and d0 + 1, in float32 (the reference's
+// COMPUTE_COS_SIN branch, ops/models/llama_v1.py:212-214).  Out of line: the range reduction of
+// sincosf is long, and inlined at every rotation change it weighed on the whole tile loop.
+template <int D>
+__device__ __noinline__ void rope_cos_sin_pair(const DecParams& p, int pos, int d0, float2& cc, float2& ss) {
+  const float t0 = (float)pos * rope_inv_freq<D>(p, d0);
+  const float t1 = (float)pos * rope_inv_freq<D>(p, d0 + 1);
+  float s0, c0, s1, c1;
+  sincosf(t0, &s0, &c0);
+  sincosf(t1, &s1, &c1);
+  cc = make_float2(c0, c1);
+  ss = make_float2(s0, s1);
+}
+
 // Forward rotation of two packed key pairs (dims d, d+1 and their partners D/2 further) in the
 // MMA's own 16-bit type: k1' = k1*c - k2*s, k2' = k1*s + k2*c, two roundings per result as the
 // reference's 16-bit evaluation has (old_ops/chunked_prefill_paged_decode.py:228-229).
@@ -231,7 +245,7 @@ __device__ __forceinline__ void store_result(const DecParams& p, int row_q, int 
 // EXTRA: the optional fusions (cache write of the new token, rotary op on the query, cos/sin
 // computed in the kernel) are compiled into a second instance of the kernel, so that the
 // plain call keeps the register budget and instruction count its bandwidth depends on.
-template <int D, int KV, bool BF16, bool MEPIC, bool EXTRA>
+template <int D, int KV, bool BF16, bool MEPIC, int EXTRA>
 __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBlocks) decode_split_kernel(DecParams p) {
   using Cfg = DecCfg<D, KV>;
   constexpr bool BF16MMA = (KV == 0) && BF16;  // fp8 caches go through f16
@@ -257,14 +271,21 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
   const int end_page = (split == p.n_splits - 1) ? npages : min(npages, first_page + p.chunk_pages);
   const bool lazy = !MEPIC && p.is_lazy != nullptr && p.is_lazy[seq] != 0;
   const int64_t* prow = MEPIC ? nullptr : p.packed + (int64_t)seq * p.packed_stride;
+  // fused rotary op: the token's position, fetched here so that only the table row's loads remain
+  // when the query is prepared
+  int64_t q_position = 0;
+  if (EXTRA && p.q_pos != nullptr) q_position = p.q_pos[row_q];
 
   if (tid == 0) {
     for (int i = 0; i < W * S; ++i) mbar_init(&bar_full[i], 1);
     mbar_fence_init();
   }
-  // ---- Q fragments (B operand: head = lane/4, four consecutive dims per k-step)
+  // ---- Q fragments (B operand: head = lane/4, four consecutive dims per k-step).  The plain
+  // call fetches them first; with the fused rotary op they are prepared after the first copies
+  // have been issued, so that the table row's latency runs under them (for the plain call that
+  // order measured 0.5 % slower).
   uint32_t qfull[KSTEPS][2], qcur[KSTEPS][2];
-  {
+  auto load_query = [&]() {
     const int h = r;
     const uint8_t* qrow = reinterpret_cast<const uint8_t*>(p.q) +
                           ((int64_t)row_q * p.q_st + (int64_t)(kvh * p.G + h) * p.q_sh) * 2;
@@ -279,7 +300,7 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
       // Fused rotary op: the query arrives without rotary embedding; rotate it forward at its
       // position (NeoX halves: dims d and d + D/2 sit in k-steps ks and ks + KSTEPS/2 of this
       // thread) and round to the query's dtype, as the stand-alone op leaves it.
-      int64_t pos = p.q_pos[row_q];
+      int64_t pos = q_position;
       if (p.cs != nullptr && pos >= p.cs_rows) pos = p.cs_rows - 1;
       const uint8_t* crow = reinterpret_cast<const uint8_t*>(p.cs) + pos * D * 2;
 #pragma unroll
@@ -287,14 +308,11 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           float2 cc, ss;
-          if (p.cs != nullptr) {
+          if (EXTRA != 2 || p.cs != nullptr) {
             cc = unpack_q<BF16>(*reinterpret_cast<const uint32_t*>(crow + (ks * 16 + c * 4 + 2 * j) * 2));
             ss = unpack_q<BF16>(*reinterpret_cast<const uint32_t*>(crow + D + (ks * 16 + c * 4 + 2 * j) * 2));
           } else {
-            const float t0 = (float)pos * rope_inv_freq<D>(p, ks * 16 + c * 4 + 2 * j);
-            const float t1 = (float)pos * rope_inv_freq<D>(p, ks * 16 + c * 4 + 2 * j + 1);
-            cc = make_float2(cosf(t0), cosf(t1));
-            ss = make_float2(sinf(t0), sinf(t1));
+            rope_cos_sin_pair<D>(p, (int)pos, ks * 16 + c * 4 + 2 * j, cc, ss);
           }
           const float2 q1 = unpack_q<BF16>(qfull[ks][j]), q2 = unpack_q<BF16>(qfull[ks + KSTEPS / 2][j]);
           qfull[ks][j] = pack_mma<BF16>(q1.x * cc.x - q2.x * ss.x, q1.y * cc.y - q2.y * ss.y);
@@ -302,7 +320,7 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
         }
       }
     }
-  }
+    };
   auto set_rotation = [&](int eff) {
     if (eff <= 1) {
 #pragma unroll
@@ -314,12 +332,12 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
       return;
     }
     int pos = eff - 1;
-    if (!(EXTRA && p.compute_cs) && pos >= p.cs_rows) pos = (int)p.cs_rows - 1;
+    if (EXTRA != 2 && pos >= p.cs_rows) pos = (int)p.cs_rows - 1;
     const uint8_t* crow = reinterpret_cast<const uint8_t*>(p.cs) + (int64_t)pos * D * 2;
 #pragma unroll
     for (int ks = 0; ks < KSTEPS / 2; ++ks) {
       // dims d = 16ks + 4c + {0..3} pair with d + D/2, which sit in k-step ks + KSTEPS/2
-      const bool compute_cs = EXTRA && p.compute_cs != 0;
+      constexpr bool compute_cs = EXTRA == 2;
       uint32_t cw[2] = {0, 0}, sw[2] = {0, 0};
       if (!compute_cs) {
         const uint2 cv = __ldg(reinterpret_cast<const uint2*>(crow + (ks * 16 + c * 4) * 2));
@@ -331,12 +349,8 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
         const float2 q1 = unpack_q<BF16>(qfull[ks][j]), q2 = unpack_q<BF16>(qfull[ks + KSTEPS / 2][j]);
         float2 cc, ss;
         if (compute_cs) {
-          // cos/sin(position * inv_freq) in float32, not rounded to the table's dtype (the
-          // reference's COMPUTE_COS_SIN branch, ops/models/llama_v1.py:212-214)
-          const float t0 = (float)(eff - 1) * rope_inv_freq<D>(p, ks * 16 + c * 4 + 2 * j);
-          const float t1 = (float)(eff - 1) * rope_inv_freq<D>(p, ks * 16 + c * 4 + 2 * j + 1);
-          cc = make_float2(cosf(t0), cosf(t1));
-          ss = make_float2(sinf(t0), sinf(t1));
+          // float32, not rounded to the table's dtype
+          rope_cos_sin_pair<D>(p, eff - 1, ks * 16 + c * 4 + 2 * j, cc, ss);
         } else {
           cc = unpack_q<BF16>(cw[j]);
           ss = unpack_q<BF16>(sw[j]);
@@ -354,7 +368,10 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
     }
   };
   int cur_eff = 1;
-  set_rotation(1);
+  if constexpr (EXTRA == 0) {
+    load_query();
+    set_rotation(1);
+  }
 
   const float k_scale = (KV != 0 && p.k_scale) ? *p.k_scale : 1.f;
   const float v_scale = (KV != 0 && p.v_scale) ? *p.v_scale : 1.f;
@@ -371,6 +388,36 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
   uint8_t* ring = smem + (size_t)warp * S * Cfg::kTileBytes;
   uint64_t* my_bar = bar_full + warp * S;
 
+  if (EXTRA && p.slots != nullptr && first_page <= npages - 1 && npages - 1 < end_page) {
+    // Fused cache write: the CTA whose run of pages holds the sequence's last page stores the new
+    // token's K/V row (in cache format) into that page before any of its copies is issued, so
+    // that this call attends to it like the calls to come.  Order: the stores, a device-wide
+    // fence by the storing threads, the CTA barrier below, a proxy fence by the thread that
+    // issues the bulk copies (which read global memory through the asynchronous proxy).
+    const int64_t slot = p.slots[row_q];
+    if (slot >= 0) {
+      constexpr int X = 16 / Cfg::kElem;  // elements per 16-byte group
+      const int64_t blk = slot >> 4;
+      const int off_g = (int)(slot & 15);
+      uint8_t* kp_g = const_cast<uint8_t*>(p.kc) + blk * p.kc_sb + (int64_t)kvh * p.kc_sh;
+      uint8_t* vp_g = const_cast<uint8_t*>(p.vc) + blk * p.vc_sb + (int64_t)kvh * p.vc_sh;
+      const uint16_t* krow = reinterpret_cast<const uint16_t*>(p.key) + (int64_t)row_q * p.k_st + (int64_t)kvh * p.k_sh;
+      const uint16_t* vrow = reinterpret_cast<const uint16_t*>(p.value) + (int64_t)row_q * p.v_st + (int64_t)kvh * p.v_sh;
+      const float ksc = (KV != 0 && p.k_scale) ? *p.k_scale : 1.f;
+      const float vsc = (KV != 0 && p.v_scale) ? *p.v_scale : 1.f;
+      for (int g = tid; g < D / X; g += Cfg::kThreads) {  // K page [D/X][16][X]
+        uint8_t grp[16];
+        to_cache_elems<KV, BF16>(krow + g * X, X, grp, ksc);
+        *reinterpret_cast<uint4*>(kp_g + (g * 16 + off_g) * 16) = *reinterpret_cast<const uint4*>(grp);
+      }
+      for (int d = tid; d < D; d += Cfg::kThreads) {      // V page [D][16]
+        uint8_t el[2];
+        to_cache_elems<KV, BF16>(vrow + d, 1, el, vsc);
+        for (int bb = 0; bb < Cfg::kElem; ++bb) vp_g[(d * 16 + off_g) * Cfg::kElem + bb] = el[bb];
+      }
+      __threadfence();
+    }
+  }
   for (int page0 = first_page; page0 < end_page && ok; page0 += p.chunk_pages) {
   const int n = min(p.chunk_pages, end_page - page0);
   // ---- page entries of this chunk: physical page, rotation in force, pad count.
@@ -441,8 +488,14 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
                 &my_bar[st]);
     }
   };
-  if (lane == 0)
+  if (lane == 0) {
+    if (EXTRA) asm volatile("fence.proxy.async;" ::: "memory");  // after the fused cache write above
     for (int it = 0; it < min(S, my_tiles); ++it) issue(it);
+  }
+  if (EXTRA != 0 && page0 == first_page) {
+    load_query();
+    set_rotation(1);
+  }
   __syncthreads();  // the rotation scan of warp 0 is complete
 
   for (int it = 0; it < my_tiles; ++it) {
@@ -454,47 +507,6 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
     if (!ok) break;
     const int pg = PPT * tl;
     const int np = min(PPT, n - pg);
-    if (EXTRA && p.slots != nullptr) {
-      // Fused cache write: the warp whose tile holds the sequence's last page puts the new
-      // token's K/V row (in cache format) into the landed copy of the page, so that this call
-      // attends to it, and into the page in global memory for the calls to come.
-      const int last = npages - 1 - (page0 + pg);  // index of the last page within this tile
-      if (last >= 0 && last < np) {
-        constexpr int X = 16 / Cfg::kElem;          // elements per 16-byte group
-        const int off_s = (seq_len - 1) & 15;
-        const int64_t slot = p.slots[row_q];
-        uint8_t* kp_s = const_cast<uint8_t*>(tile) + last * Cfg::kPageBytes;
-        uint8_t* vp_s = const_cast<uint8_t*>(tile) + (PPT + last) * Cfg::kPageBytes;
-        uint8_t* kp_g = nullptr;
-        uint8_t* vp_g = nullptr;
-        int off_g = 0;
-        if (slot >= 0) {
-          const int64_t blk = slot >> 4;
-          off_g = (int)(slot & 15);
-          kp_g = const_cast<uint8_t*>(p.kc) + blk * p.kc_sb + (int64_t)kvh * p.kc_sh;
-          vp_g = const_cast<uint8_t*>(p.vc) + blk * p.vc_sb + (int64_t)kvh * p.vc_sh;
-        }
-        const uint16_t* krow = reinterpret_cast<const uint16_t*>(p.key) + (int64_t)row_q * p.k_st + (int64_t)kvh * p.k_sh;
-        const uint16_t* vrow = reinterpret_cast<const uint16_t*>(p.value) + (int64_t)row_q * p.v_st + (int64_t)kvh * p.v_sh;
-        const float ksc = (KV != 0 && p.k_scale) ? *p.k_scale : 1.f;
-        const float vsc = (KV != 0 && p.v_scale) ? *p.v_scale : 1.f;
-        for (int g = lane; g < D / X; g += 32) {      // K page [D/X][16][X]
-          uint8_t grp[16];
-          to_cache_elems<KV, BF16>(krow + g * X, X, grp, ksc);
-          *reinterpret_cast<uint4*>(kp_s + (g * 16 + off_s) * 16) = *reinterpret_cast<const uint4*>(grp);
-          if (kp_g) *reinterpret_cast<uint4*>(kp_g + (g * 16 + off_g) * 16) = *reinterpret_cast<const uint4*>(grp);
-        }
-        for (int d = lane; d < D; d += 32) {          // V page [D][16]
-          uint8_t el[2];
-          to_cache_elems<KV, BF16>(vrow + d, 1, el, vsc);
-          for (int bb = 0; bb < Cfg::kElem; ++bb) {
-            vp_s[(d * 16 + off_s) * Cfg::kElem + bb] = el[bb];
-            if (vp_g) vp_g[(d * 16 + off_g) * Cfg::kElem + bb] = el[bb];
-          }
-        }
-        __syncwarp();
-      }
-    }
     float s[PPT][4];
     bool vlo[PPT], vhi[PPT];
 #pragma unroll
@@ -770,7 +782,7 @@ int quantum_for(const LaDecodeArgs& a) {
   return 4 * (page_bytes > 2048 ? 1 : 2);
 }
 
-template <int D, int KV, bool BF16, bool MEPIC, bool EXTRA>
+template <int D, int KV, bool BF16, bool MEPIC, int EXTRA>
 int launch_dec_m(const LaDecodeArgs& a, DecParams& p, cudaStream_t stream) {
   using Cfg = DecCfg<D, KV>;
   auto kern = decode_split_kernel<D, KV, BF16, MEPIC, EXTRA>;
@@ -797,10 +809,13 @@ int launch_dec_m(const LaDecodeArgs& a, DecParams& p, cudaStream_t stream) {
 
 template <int D, int KV, bool BF16>
 int launch_dec(const LaDecodeArgs& a, DecParams& p, cudaStream_t stream) {
-  const bool extra = a.slot_mapping != nullptr || a.q_positions != nullptr || a.compute_cos_sin != 0;
+  // 0: the plain call; 1: with the fused cache write and / or the rotary op on the query (table
+  // rows); 2: cos/sin evaluated in the kernel as well (per-page rotation mode only)
+  const bool extra = a.slot_mapping != nullptr || a.q_positions != nullptr;
   if (a.rot_mode == LA_ROT_MEPIC)
-    return extra ? launch_dec_m<D, KV, BF16, true, true>(a, p, stream) : launch_dec_m<D, KV, BF16, true, false>(a, p, stream);
-  return extra ? launch_dec_m<D, KV, BF16, false, true>(a, p, stream) : launch_dec_m<D, KV, BF16, false, false>(a, p, stream);
+    return extra ? launch_dec_m<D, KV, BF16, true, 1>(a, p, stream) : launch_dec_m<D, KV, BF16, true, 0>(a, p, stream);
+  if (a.compute_cos_sin != 0) return launch_dec_m<D, KV, BF16, false, 2>(a, p, stream);
+  return extra ? launch_dec_m<D, KV, BF16, false, 1>(a, p, stream) : launch_dec_m<D, KV, BF16, false, 0>(a, p, stream);
 }
 
 }  // namespace

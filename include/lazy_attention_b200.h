@@ -214,7 +214,8 @@ typedef struct LaDecodeArgs {
   /* Optional fused cache write for the decode rows: key / value [num_tokens, Hkv, D] of the
    * step and slot_mapping int64 [num_tokens].  When slot_mapping is non-NULL the kernel
    * stores each sequence's new K/V row into the caches (as la_write_paged_cache would have
-   * before the call) and attends to it; seq_lens counts the new token, as in the reference. */
+   * before the call: a negative slot is skipped) and attends to what the page then holds;
+   * seq_lens counts the new token, as in the reference. */
   const void* key;
   const void* value;
   int64_t k_stride_t, k_stride_h, v_stride_t, v_stride_h;

@@ -437,7 +437,7 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
     if (p.num_blocks > 0) blk = max(0, min(blk, (int)p.num_blocks - 1));
     const int rot = lazy ? (int)((pk >> 16) & 0xFFFF) : 1;
     const int pad = (lazy && !p.ignore_q_mask) ? min((int)(pk & 0xFFFF), 16) : 0;
-    ent[i] = make_int2(blk, (rot << 16) | pad);
+    ent[i] = make_int2(blk, (int)(((uint32_t)rot << 16) | (uint32_t)pad));
   }
   __syncthreads();
   if (warp == 0 && lazy) {
@@ -459,7 +459,7 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
       const int i = g0 + lane;
       int2 e = make_int2(0, 0);
       if (i < n) e = ent[i];
-      int eff = e.y >> 16;
+      int eff = (int)((uint32_t)e.y >> 16);  // the rotation field fills the top 16 bits: no sign extension
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int up = __shfl_up_sync(0xffffffffu, eff, o);
@@ -467,7 +467,7 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
       }
       if (eff == 0) eff = carry;
       carry = __shfl_sync(0xffffffffu, eff, 31);
-      if (i < n) ent[i] = make_int2(e.x, (eff << 16) | (e.y & 0xFFFF));
+      if (i < n) ent[i] = make_int2(e.x, (int)(((uint32_t)eff << 16) | ((uint32_t)e.y & 0xFFFFu)));
     }
   }
 
@@ -516,7 +516,7 @@ __global__ void __launch_bounds__(DecCfg<D, KV>::kThreads, DecCfg<D, KV>::kMinBl
       vlo[i] = vhi[i] = false;
       if (i < np) {
         const int2 e = ent[pg + i];
-        const int eff = e.y >> 16, pad = e.y & 0xFFFF;
+        const int eff = (int)((uint32_t)e.y >> 16), pad = e.y & 0xFFFF;
         if (eff != cur_eff) {
           set_rotation(eff);
           cur_eff = eff;

@@ -521,3 +521,29 @@ def test_cos_sin_table(llama3, dtype):
     bound = 2e-6 + pos * 2.4e-7 + (4e-3 if dtype == torch.bfloat16 else 0.0)
     assert bool(((got - want).abs() <= bound).all())
     assert torch.equal(got[0, :64], torch.ones(64)) and torch.equal(got[0, 64:], torch.zeros(64))
+
+
+@pytest.mark.parametrize("variant,op", [("lazy", "lazy_op")])
+@pytest.mark.parametrize("kv", ["auto", "fp8_e4m3"])
+def test_rotation_offsets_at_the_16_bit_limit(variant, op, kv):
+    """Pages whose rotation offset is the largest the packed table can carry (65535, i.e. row
+    65534 of the cos/sin table), in a prefill request and in a decode row: the offset must
+    survive the 16-bit field of the packed entry and reach the table lookup intact."""
+    import lazy_attention_b200 as la
+    reqs = [dict(docs=[2, 0, 1], qlen=130), dict(docs=[3, 1], qlen=1), dict(docs=[5, 4], qlen=40)]
+    ks, vs = (0.11, 0.07) if "fp8" in kv else (1.0, 1.0)
+    case = synth.build_prefill(synth.GEOM_8B, torch.bfloat16, POOL, reqs, seed=17, variant=variant, device="cuda",
+                               kv_dtype=kv, k_scale=ks, v_scale=vs, max_position=la.MAX_PACKED_Q_OFFSET + 1)
+    assert case["cos_sin_cache"].shape[0] == la.MAX_PACKED_Q_OFFSET + 1
+    off = case["q_offset"]
+    for b in range(off.shape[0]):
+        rows = torch.nonzero(off[b] > 1).flatten()
+        assert rows.numel() > 0
+        off[b, rows[-1]] = la.MAX_PACKED_Q_OFFSET          # the last rotating page of the request
+        off[b, rows[0]] = la.MAX_PACKED_Q_OFFSET - 1
+        off[b, rows[rows.numel() // 2]] = 32768             # the first value with the field's top bit set
+    case["packed_block_table"] = util.pack_host(case).cuda()
+    want = util.run_oracle(case, op)
+    for kernel in ("tensor", "general"):
+        got = util.run_cuda(case, op, kernel=kernel)
+        util.assert_close(got, want, what=f"offsets at the limit, {kv}, {kernel}", **(FP8 if "fp8" in kv else HALF))

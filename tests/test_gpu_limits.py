@@ -1,0 +1,74 @@
+"""Edge cases of sizes and table fields, tensor-core / split-KV kernels and the general kernel
+against the oracle: a decode batch behind ~61k cached tokens (rotation offsets far above 32767),
+pages that are padding from the first slot on, sequences without any cached context, and
+one-token requests through the prefill operator."""
+import pytest
+import torch
+
+import util
+from lazy_attention_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+HALF = dict(atol=2e-2, rtol=1e-2)
+FP8 = dict(atol=5e-2, rtol=1e-2)
+POOL = [100, 64, 33, 250, 16, 129]
+
+
+@pytest.mark.parametrize("kv", ["auto", "fp8_e4m3"])
+@pytest.mark.parametrize("variant,op", [("lazy", "lazy_op"), ("mepic", "mepic_op")])
+def test_decode_behind_sixty_thousand_tokens(kv, variant, op):
+    docs = [[512] * 120, [512] * 70 + [100, 37], [300] * 3]
+    scales = dict(k_scale=0.12, v_scale=0.08) if "fp8" in kv else {}
+    case = synth.build_decode(synth.GEOM_8B, torch.bfloat16, docs, seed=41, device="cuda", kv_dtype=kv,
+                              variant=variant, **scales)
+    if variant == "lazy":
+        assert int(case["q_offset"].max()) > 40000
+    case["packed_block_table"] = util.pack_host(case).cuda()
+    want = util.run_oracle(case, op)
+    for kernel in ("tensor", "general"):
+        got = util.run_cuda(case, op, kernel=kernel)
+        util.assert_close(got, want, what=f"long decode {kv} {variant} {kernel}", **(FP8 if "fp8" in kv else HALF))
+
+
+@pytest.mark.parametrize("kv", ["auto", "fp8_e4m3"])
+def test_pages_that_are_all_padding(kv):
+    """q_mask = 16 on some pages (every slot is padding), next to partly padded ones."""
+    reqs = [dict(docs=[2, 0, 1], qlen=130), dict(docs=[3, 1, 4], qlen=1), dict(docs=[5, 4], qlen=40)]
+    ks, vs = (0.11, 0.07) if "fp8" in kv else (1.0, 1.0)
+    case = synth.build_prefill(synth.GEOM_8B, torch.bfloat16, POOL, reqs, seed=19, variant="lazy", device="cuda",
+                               kv_dtype=kv, k_scale=ks, v_scale=vs)
+    ctx_pages = ((case["seq_lens"] - (case["query_start_loc"][1:] - case["query_start_loc"][:-1])) // 16).cpu()
+    for b in range(len(reqs)):
+        n = int(ctx_pages[b])
+        case["q_mask"][b, 1] = 16
+        case["q_mask"][b, n // 2] = 16
+        case["q_mask"][b, n - 1] = 16   # the last whole page of the context
+    case["packed_block_table"] = util.pack_host(case).cuda()
+    want = util.run_oracle(case, "lazy_op")
+    for kernel in ("tensor", "general"):
+        got = util.run_cuda(case, "lazy_op", kernel=kernel)
+        util.assert_close(got, want, what=f"all-padding pages {kv} {kernel}", **(FP8 if "fp8" in kv else HALF))
+
+
+@pytest.mark.parametrize("variant,op", [("lazy", "lazy_op"), ("mepic", "mepic_op")])
+def test_sequences_without_cached_context(variant, op):
+    """Decode rows and prefill requests whose only keys are their own new tokens."""
+    reqs = [dict(docs=[], qlen=1), dict(docs=[], qlen=300), dict(docs=[2], qlen=1), dict(docs=[], qlen=17)]
+    case = synth.build_prefill(synth.GEOM_8B, torch.bfloat16, POOL, reqs, seed=23, variant=variant, device="cuda")
+    case["packed_block_table"] = util.pack_host(case).cuda()
+    want = util.run_oracle(case, op)
+    for kernel in ("tensor", "general"):
+        got = util.run_cuda(case, op, kernel=kernel)
+        util.assert_close(got, want, what=f"no context {variant} {kernel}", **HALF)
+
+
+def test_one_token_requests_through_the_prefill_operator():
+    """context_attention_fwd with skip_decode off computes one-token requests itself."""
+    reqs = [dict(docs=[2, 0], qlen=1), dict(docs=[3, 1, 5], qlen=260), dict(docs=[4], qlen=1)]
+    case = synth.build_prefill(synth.GEOM_8B, torch.bfloat16, POOL, reqs, seed=29, variant="lazy", device="cuda")
+    case["packed_block_table"] = util.pack_host(case).cuda()
+    want = util.run_oracle(case, "lazy_prefill")
+    for kernel in ("tensor", "general"):
+        got = util.run_cuda(case, "lazy_prefill", kernel=kernel)
+        util.assert_close(got, want, what=f"one-token requests {kernel}", **HALF)

@@ -114,3 +114,31 @@ def test_fused_gather_equals_all_gather():
         assert ok_prefill, f"rank {rank}: prefill rows stored by the peers differ from the all-gather"
         assert ok_decode, f"rank {rank}: decode rows stored by the peers differ from the all-gather"
     assert all(p.exitcode == 0 for p in procs)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tensors_on_a_device_that_is_not_current():
+    """One process, tensors on cuda:1 while cuda:0 is current: the operators launch on the
+    tensors' device and stream (tensor maps, status word, kernel attributes are per device)."""
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import lazy_attention_b200 as la
+    from lazy_attention_b200 import synth
+    import util
+    assert torch.cuda.current_device() == 0
+    pool = [100, 64, 33, 250, 16, 129]
+    reqs = [dict(docs=[2, 0, 1], qlen=37), dict(docs=[3, 1, 5], qlen=300), dict(docs=[1, 2, 4], qlen=1)]
+    for dev in ("cuda:1", "cuda:0", "cuda:1"):
+        case = synth.build_prefill(synth.GEOM_8B, torch.bfloat16, pool, reqs, seed=7, variant="lazy", device=dev)
+        case["packed_block_table"] = util.pack_host(case).to(dev)
+        out = util.new_out(case)
+        la.chunked_prefill_paged_decode(
+            case["q"], case["k"], case["v"], out, case["kv_cache_dtype"], case["k_cache"], case["v_cache"],
+            case["block_table"], case["query_start_loc"], case["seq_lens"], case["max_seq_len"], case["max_query_len"],
+            case["k_scale"], case["v_scale"], sm_scale=case["sm_scale"], cos_sin_cache=case["cos_sin_cache"],
+            is_lazy=case["is_lazy"], q_offset=case["q_offset"], q_mask=case["q_mask"],
+            packed_block_table=case["packed_block_table"], kernel="tensor")
+        torch.cuda.synchronize(dev)
+        assert torch.cuda.current_device() == 0
+        with torch.cuda.device(dev):
+            assert la.device_status() == 0
+        util.assert_close(out.float().cpu(), util.run_oracle(case, "lazy_op"), atol=2e-2, rtol=1e-2, what=f"on {dev}")

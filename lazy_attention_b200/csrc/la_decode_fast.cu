@@ -855,6 +855,9 @@ size_t fast_decode_workspace_bytes(const LaDecodeArgs& a) {
 
 int launch_fast_decode(const LaDecodeArgs& a, cudaStream_t stream) {
   const DecPlan pl = make_dec_plan(a, quantum_for(a));
+  LA_REQUIRE(a.num_seqs <= 65535 && a.num_kv_heads <= 65535, LA_ERR_UNSUPPORTED,
+             "la_decode_fwd: %d sequences or %d KV heads exceed the launch grid (at most 65535 each)", a.num_seqs,
+             a.num_kv_heads);
   const int e = a.kv_dtype == a.q_dtype ? 2 : 1;
   DecParams p{};
   p.q = a.q; p.out = a.out;

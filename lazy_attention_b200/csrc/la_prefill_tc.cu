@@ -1852,6 +1852,9 @@ int launch_tc(const LaPrefillArgs& a, const TcParams& p, const MapPair& mp, cons
 int launch_tc_with_scratch(const LaPrefillArgs& a, cudaStream_t stream, void* scratch, size_t scratch_bytes,
                            bool keep_maps, const char* who) {
   const TcPlan pl = make_plan(a);
+  LA_REQUIRE((int64_t)a.batch * pl.n_splits <= 65535 && a.num_kv_heads <= 65535, LA_ERR_UNSUPPORTED,
+             "%s: %d requests x %d splits (at most 65535) or %d KV heads (at most 65535) exceed the launch grid",
+             who, a.batch, pl.n_splits, a.num_kv_heads);
   // The scratch is checked before anything touches the device, so that a caller who
   // forgot the workspace learns the size from the error text.
   LA_REQUIRE(pl.scratch_bytes == 0 || (scratch != nullptr && scratch_bytes >= pl.scratch_bytes), LA_ERR_WORKSPACE,

@@ -92,6 +92,17 @@ def test_missing_workspace_is_an_error_not_a_slow_path():
     assert lib.la_prefill_fwd_noalloc(None, None) == _lib.LA_ERR_INVALID_ARGUMENT
 
 
+def test_a_batch_beyond_the_launch_grid_is_refused():
+    """More requests x splits than a grid dimension holds: a status code with the numbers, before
+    anything touches the device."""
+    lib = _lib.load()
+    a = _split_prefill_args()
+    a.batch = 70000
+    a.kernel = _lib.KERNEL_TENSOR
+    assert lib.la_prefill_fwd(ctypes.byref(a), None) == _lib.LA_ERR_UNSUPPORTED
+    assert "70000" in _lib.last_error() and "65535" in _lib.last_error()
+
+
 def test_patch_in_binds_what_the_reference_backend_passes():
     """The keyword sets the reference backend passes to its two operators, and the modules it
     imports them from, were read from its source when the fixtures were made

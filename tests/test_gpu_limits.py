@@ -44,6 +44,10 @@ def test_pages_that_are_all_padding(kv):
         case["q_mask"][b, 1] = 16
         case["q_mask"][b, n // 2] = 16
         case["q_mask"][b, n - 1] = 16   # the last whole page of the context
+    # a whole 128-key tile of padding at the start of a request (its running maximum starts at
+    # -inf) and in the middle of a decode row (whole tiles of the split-KV kernel)
+    case["q_mask"][0, 0:8] = 16
+    case["q_mask"][1, 8:16] = 16
     case["packed_block_table"] = util.pack_host(case).cuda()
     want = util.run_oracle(case, "lazy_op")
     for kernel in ("tensor", "general"):

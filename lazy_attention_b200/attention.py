@@ -52,10 +52,11 @@ def launch_count() -> int:
 
 
 def _workspace(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
-    """Scratch for the split-KV kernels, owned by this module, grown on demand."""
+    """Scratch for the split-KV kernels, owned by this module, grown on demand: one buffer per
+    device and stream, so that calls on different streams never share partial results."""
     if nbytes <= 0:
         return None
-    key = (device.type, device.index)
+    key = (device.type, device.index, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         if ws is not None:
@@ -66,10 +67,9 @@ def _workspace(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
 
 
 def reserve_workspace(device, nbytes: int) -> None:
-    """Grow this device's split-KV scratch to at least ``nbytes`` now, e.g. before a
-    CUDA-graph capture, so that later calls do not move it.  The scratch is shared
-    by all calls on the device: calls that may overlap on different streams must
-    not both split the KV range."""
+    """Grow the split-KV scratch of this device's current stream to at least ``nbytes`` now,
+    e.g. before a CUDA-graph capture, so that later calls do not move it.  Calls on one stream
+    share it (they are ordered); every other stream gets a buffer of its own."""
     _workspace(torch.device(device), int(nbytes))
 
 

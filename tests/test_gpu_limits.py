@@ -76,3 +76,33 @@ def test_one_token_requests_through_the_prefill_operator():
     for kernel in ("tensor", "general"):
         got = util.run_cuda(case, "lazy_prefill", kernel=kernel)
         util.assert_close(got, want, what=f"one-token requests {kernel}", **HALF)
+
+
+def test_calls_on_two_streams_keep_their_partial_results_apart(monkeypatch):
+    """Two split-KV calls in flight on two streams: each stream has its own scratch, so the
+    results equal those of the calls run one after the other."""
+    monkeypatch.setenv("LAZY_ATTN_B200_PREFILL_SPLITS", "4")
+    cases = []
+    for seed in (51, 52):
+        reqs = [dict(docs=[2, 0, 1, 3, 5], qlen=300), dict(docs=[3, 1, 5, 0], qlen=260)]
+        case = synth.build_prefill(synth.GEOM_8B, torch.bfloat16, [700, 640, 333, 900, 160, 1290], reqs, seed=seed,
+                                   variant="lazy", device="cuda")
+        case["packed_block_table"] = util.pack_host(case).cuda()
+        cases.append(case)
+    alone = [util.run_cuda(c, "lazy_prefill", kernel="tensor") for c in cases]
+    import lazy_attention_b200 as la
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [util.new_out(c) for c in cases]
+    torch.cuda.synchronize()
+    for _ in range(20):
+        for c, o, s in zip(cases, outs, streams):
+            with torch.cuda.stream(s):
+                la.context_attention_fwd(c["q"], c["k"], c["v"], o, c["kv_cache_dtype"], c["k_cache"], c["v_cache"],
+                                         c["block_table"], c["query_start_loc"], c["seq_lens"], c["max_seq_len"],
+                                         c["max_query_len"], c["k_scale"], c["v_scale"], sm_scale=c["sm_scale"],
+                                         cos_sin_cache=c["cos_sin_cache"], is_lazy=c["is_lazy"], q_offset=c["q_offset"],
+                                         q_mask=c["q_mask"], kernel="tensor")
+    torch.cuda.synchronize()
+    assert la.device_status() == 0
+    for o, a in zip(outs, alone):
+        assert torch.equal(o.float().cpu(), a), "a call's result changed when another stream's call ran beside it"

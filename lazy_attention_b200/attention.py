@@ -56,6 +56,10 @@ def _workspace(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
     device and stream, so that calls on different streams never share partial results."""
     if nbytes <= 0:
         return None
+    if torch.cuda.is_current_stream_capturing():
+        # like any temporary of a captured region: it lives in the graph's memory pool, stays
+        # reserved for the graph's replays and goes with the graph
+        return torch.empty(int(nbytes) + 256, dtype=torch.uint8, device=device)
     key = (device.type, device.index, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:

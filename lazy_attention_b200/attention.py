@@ -71,9 +71,10 @@ def _workspace(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
 
 
 def reserve_workspace(device, nbytes: int) -> None:
-    """Grow the split-KV scratch of this device's current stream to at least ``nbytes`` now,
-    e.g. before a CUDA-graph capture, so that later calls do not move it.  Calls on one stream
-    share it (they are ordered); every other stream gets a buffer of its own."""
+    """Grow the split-KV scratch of this device's current stream to at least ``nbytes`` now, so
+    that later calls do not allocate.  Calls on one stream share it (they are ordered); every
+    other stream gets a buffer of its own; a call made under stream capture takes a temporary
+    from the graph's memory pool instead."""
     _workspace(torch.device(device), int(nbytes))
 
 

@@ -114,3 +114,40 @@ def test_argument_errors_match_reference():
     with pytest.raises(NotImplementedError, match="Alibi"):
         la.context_attention_fwd(*args, "auto", case["k_cache"], case["v_cache"], *rest,
                                  alibi_slopes=torch.ones(4))
+
+
+def test_metadata_properties_hold_for_random_document_sets():
+    """Properties the kernels rely on, over random document sets (hypothesis): one entry per
+    page plus the query page; the largest offset is what max_rotation_offset announces; offsets
+    never decrease from one document to the next; every pad count is below a page and sits on
+    its document's last page; the per-token variant has the same pads and no offsets."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=200, deadline=None)
+    @given(st.lists(st.integers(min_value=1, max_value=3000), min_size=0, max_size=12),
+           st.sampled_from([16, 32]))
+    def check(lens, bs):
+        padded = [(n + bs - 1) // bs * bs for n in lens]
+        off, msk = la.metadata_for_lazy_attention(lens, padded, bs)
+        pages = sum(padded) // bs
+        assert len(off) == len(msk) == pages + 1
+        assert off[-1] == 1 and msk[-1] == 0
+        if lens:
+            assert max(off[:-1]) == la.max_rotation_offset(lens, padded)
+            assert all(a <= b for a, b in zip(off[:-2], off[1:-1]))
+        cursor = 0
+        for n, p in zip(lens, padded):
+            k = p // bs
+            assert len(set(off[cursor:cursor + k])) == 1, "one offset per document"
+            assert all(m == 0 for m in msk[cursor:cursor + k - 1])
+            assert msk[cursor + k - 1] == p - n and 0 <= p - n < bs
+            cursor += k
+        off_m, msk_m = la.metadata_for_mepic(lens, padded, bs)
+        assert msk_m == msk and not any(off_m)
+        if lens and la.max_rotation_offset(lens, padded) > la.MAX_PACKED_Q_OFFSET:
+            with pytest.raises(ValueError):
+                la.validate_rotation_offsets(lens, padded)
+        else:
+            la.validate_rotation_offsets(lens, padded)
+
+    check()

@@ -106,3 +106,33 @@ def test_calls_on_two_streams_keep_their_partial_results_apart(monkeypatch):
     assert la.device_status() == 0
     for o, a in zip(outs, alone):
         assert torch.equal(o.float().cpu(), a), "a call's result changed when another stream's call ran beside it"
+
+
+def test_per_token_operator_with_absolute_rotation_off_at_large_offsets():
+    """``is_mepic=False`` rotates a page's tokens at ``q_offset - 1 + slot``: offsets far above
+    32767, D = 128 and 64, through the prefill operator and the dispatch operator."""
+    for geom in (synth.GEOM_8B, synth.GEOM_1B):
+        reqs = [dict(docs=[2, 0, 1], qlen=130), dict(docs=[5, 4], qlen=40)]
+        case = synth.build_prefill(geom, torch.bfloat16, POOL, reqs, seed=31, variant="mepic", device="cuda",
+                                   max_position=65536)
+        off = case["q_offset"]
+        for b in range(off.shape[0]):
+            pages = int((case["seq_lens"][b] - (case["query_start_loc"][b + 1] - case["query_start_loc"][b])) // 16)
+            off[b, :pages] = torch.randint(30000, 65000, (pages,), generator=torch.Generator().manual_seed(b)).to(off)
+        want = util.run_oracle(case, "mepic_prefill", is_mepic=False)
+        for kernel in ("tensor", "general"):
+            got = util.run_cuda(case, "mepic_prefill", kernel=kernel, is_mepic=False)
+            util.assert_close(got, want, what=f"absolute rotation off, d{geom.head_dim}, {kernel}", **HALF)
+
+
+@pytest.mark.parametrize("dtype,kv", [(torch.float16, "auto"), (torch.float16, "fp8_e5m2"), (torch.bfloat16, "fp8_e5m2")])
+def test_long_decode_at_head_dim_64(dtype, kv):
+    """1B geometry (1 KB fp8 pages: four pages per tile), contexts up to ~40k tokens."""
+    docs = [[512] * 80, [700] * 9 + [33], [16] * 5, [2048] * 12]
+    scales = dict(k_scale=0.12, v_scale=0.08) if "fp8" in kv else {}
+    case = synth.build_decode(synth.GEOM_1B, dtype, docs, seed=43, device="cuda", kv_dtype=kv, **scales)
+    case["packed_block_table"] = util.pack_host(case).cuda()
+    want = util.run_oracle(case, "lazy_op")
+    for kernel in ("tensor", "general"):
+        got = util.run_cuda(case, "lazy_op", kernel=kernel)
+        util.assert_close(got, want, what=f"long decode d64 {dtype} {kv} {kernel}", **(FP8 if "fp8" in kv else HALF))

@@ -95,3 +95,40 @@ def test_c5_full_size():
     ones = util.run_cuda(case, "lazy_op", kernel="tensor")
     vs = float(case["v_scale"].reshape(-1)[0])
     assert float((ones / vs - 1.0).abs().max()) < 1e-2
+
+
+def test_c5_fused_cache_write_at_full_size():
+    """The decode call that stores the new tokens' rows itself (2048 CTAs store a row and then
+    copy the page that holds it, with the memory system saturated) must give, bit for bit, the
+    result of a separate cache write followed by the plain call."""
+    import lazy_attention_b200 as la
+    case = synth.config_c5(device="cuda")
+    case["packed_block_table"] = util.pack_host(case).cuda()
+    bt, seq = case["block_table"].cpu(), case["seq_lens"].cpu()
+    slots = torch.tensor([int(bt[b, (int(seq[b]) - 1) // 16]) * 16 + (int(seq[b]) - 1) % 16 for b in range(len(seq))],
+                         dtype=torch.int64).cuda()
+
+    def run(slot_mapping, key, value):
+        out = util.new_out(case)
+        la.chunked_prefill_paged_decode(
+            case["q"], key, value, out, case["kv_cache_dtype"], case["k_cache"], case["v_cache"], case["block_table"],
+            case["query_start_loc"], case["seq_lens"], case["max_seq_len"], 1, case["k_scale"], case["v_scale"],
+            sm_scale=case["sm_scale"], cos_sin_cache=case["cos_sin_cache"], is_lazy=case["is_lazy"],
+            q_offset=case["q_offset"], q_mask=case["q_mask"], packed_block_table=case["packed_block_table"],
+            kernel="tensor", slot_mapping=slot_mapping)
+        torch.cuda.synchronize()
+        assert la.device_status() == 0
+        return out
+
+    before = run(None, case["k"], case["v"])
+    for rep in range(3):
+        g = torch.Generator(device="cuda").manual_seed(rep)
+        key = (torch.randn(case["k"].shape, generator=g, device="cuda") * 1.2).to(case["k"].dtype)
+        value = (torch.randn(case["v"].shape, generator=g, device="cuda") * 1.2).to(case["v"].dtype)
+        fused = run(slots, key, value)          # the caches are several GB: written in place, no copies
+        la.write_to_paged_cache(key, value, case["k_cache"], case["v_cache"], slots, case["kv_cache_dtype"],
+                                case["k_scale"], case["v_scale"])
+        separate = run(None, key, value)
+        assert torch.equal(fused, separate), f"repetition {rep}: the call did not attend to the rows it stored"
+        assert not torch.equal(fused, before)
+        before = separate
